@@ -283,15 +283,16 @@ def _number(d: dict, key: str, where: str, positive: bool = True) -> float:
 
 @dataclass
 class RotationConfig:
-  """``rot``: ``dims`` rotated values of a head, ``base`` of the frequencies, and optionally ``scaling`` {factor, original,
-  fast, slow} (frequencies stretched for contexts beyond ``original``)."""
+  """``rot``: ``dims`` rotated values of a head, ``base`` of the frequencies, and optionally ``scaling``: the numbers that
+  stretch the frequencies for contexts beyond ``original`` - {factor, original, fast, slow} by default, or the keys the
+  design names (``scaling_keys``)."""
 
   dims: int
   base: float
   scaling: Optional[Dict[str, float]] = None
 
   @classmethod
-  def read(cls, m: dict, where: str) -> "RotationConfig":
+  def read(cls, m: dict, where: str, scaling_keys=("factor", "original", "fast", "slow")) -> "RotationConfig":
     rot = m.get("rot")
     if not isinstance(rot, dict):
       raise ConfigError(f"{where}.rot is missing")
@@ -303,7 +304,7 @@ class RotationConfig:
     if scaling is not None:
       if not isinstance(scaling, dict):
         raise ConfigError(f"{where}.rot.scaling must be an object")
-      scaling = {k: _number(scaling, k, f"{where}.rot.scaling") for k in ("factor", "original", "fast", "slow")}
+      scaling = {k: _number(scaling, k, f"{where}.rot.scaling") for k in scaling_keys}
     return cls(dims, base, scaling)
 
 
@@ -491,6 +492,155 @@ class VugudraConfig(ModelConfig):
          "layers": [dict(x) for x in self.layers]}
     if self.loop is not None:
       d["loop"] = dict(self.loop)
+    if self.low_ranks:
+      d["low_ranks"] = dict(self.low_ranks)
+    d.update(self.extra)
+    return d
+
+
+@dataclass
+class GatedLinearAttentionConfig:
+  """``layers[i].mixer`` of a ``gla`` layer.  The low rank of the decay's projection is read from the tensors' shapes."""
+
+  heads: int
+  dim: int
+  vdim: int
+  tau: float
+
+
+@dataclass
+class BiasedAttentionConfig:
+  """The left member of a Famupel ``parallel`` layer's mixer: grouped-query softmax attention over every earlier token."""
+
+  heads: int
+  kv_heads: int
+  dim: int
+  vdim: int
+  scale: float
+  rot: RotationConfig
+
+
+@dataclass
+class RetentionConfig:
+  """The right member of a Famupel ``parallel`` layer's mixer: linear attention with one fixed decay a head."""
+
+  heads: int
+  dim: int
+  vdim: int
+  decay: List[float]
+  rot: RotationConfig
+
+
+@dataclass
+class FamupelConfig(ModelConfig):
+  """Famupel: a decoder whose layers are listed one by one (``layers[i].{type, mixer, mlp}``), each a pre-norm layer of a
+  mixer and a dense squared-ReLU feed-forward (or none); mixers of two types - ``gla`` (gated linear attention) and
+  ``parallel`` (biased softmax attention with an output gate beside a retention, summed with ``left_scale`` and
+  ``right_scale``).  With ``streams`` the residual stream is that many streams that every sublayer reads as a weighted sum
+  and writes through a mixing matrix (hyper-connections); without it the residual sum is the usual one.  Other keys:
+  ``architecture``, ``vocab``, ``width``, ``norm.eps``.  ``low_ranks`` is not a key of the file: the rank of a gla layer's
+  decay projection is given by a tensor's shape only, and the loader of the configuration reads it from the weights file's
+  header.  The design has no position limit of its own; ``max_position_embeddings`` is only the engine's bound."""
+
+  architecture: str = "Famupel"
+  vocab: int = 0
+  width: int = 0
+  norm: Dict[str, Any] = field(default_factory=dict)
+  streams: Optional[int] = None
+  layers: List[Dict[str, Any]] = field(default_factory=list)
+  max_position_embeddings: int = 1 << 30
+  initializer_range: float = 0.02
+  low_ranks: Optional[Dict[str, int]] = None      # "l<i>.decay" -> rank, when known
+
+  TYPES = ("gla", "parallel")
+  SCALING_KEYS = ("factor", "low", "high", "original")
+
+  def validate(self) -> None:
+    if not self.architectures:
+      self.architectures = [self.architecture]
+    self.vocab_size = self.vocab
+    for key in ("vocab", "width"):
+      v = getattr(self, key)
+      if not isinstance(v, int) or isinstance(v, bool) or v <= 0:
+        raise ConfigError(f"{key} must be a positive integer, got {v!r}")
+    eps = self.norm.get("eps") if isinstance(self.norm, dict) else None
+    if not isinstance(eps, (int, float)) or not eps > 0:
+      raise ConfigError(f"norm.eps must be a positive number, got {eps!r}")
+    if self.streams is not None and (not isinstance(self.streams, int) or isinstance(self.streams, bool) or self.streams <= 0):
+      raise ConfigError(f"streams must be a positive integer or absent, got {self.streams!r}")
+    if not self.layers:
+      raise ConfigError("layers must list at least one layer")
+    for i in range(len(self.layers)):
+      self.mixer_of(i)
+      self.ff_of(i)
+
+  @property
+  def norm_eps(self) -> float:
+    return float(self.norm["eps"])
+
+  def type_of(self, i: int) -> str:
+    kind = self.layers[i].get("type")
+    if kind not in self.TYPES:
+      raise ConfigError(f"layers[{i}].type={kind!r} is not a mixer of this design (known: {', '.join(self.TYPES)})")
+    return kind
+
+  def mixer_of(self, i: int):
+    """The typed mixer configuration of layer ``i``: a ``GatedLinearAttentionConfig`` or, for a ``parallel`` layer, the
+    tuple (``BiasedAttentionConfig``, ``RetentionConfig``, left_scale, right_scale)."""
+    kind = self.type_of(i)
+    m = self.layers[i].get("mixer")
+    where = f"layers[{i}].mixer"
+    if not isinstance(m, dict):
+      raise ConfigError(f"{where} is missing")
+    if kind == "gla":
+      return GatedLinearAttentionConfig(*(_positive_int(m, k, where) for k in ("heads", "dim", "vdim")), _number(m, "tau", where))
+    left, right = m.get("left"), m.get("right")
+    if not isinstance(left, dict) or not isinstance(right, dict):
+      raise ConfigError(f"{where} of a parallel layer needs 'left' and 'right'")
+    lw, rw = where + ".left", where + ".right"
+    lc = BiasedAttentionConfig(*(_positive_int(left, k, lw) for k in ("heads", "kv_heads", "dim", "vdim")), _number(left, "scale", lw),
+                               RotationConfig.read(left, lw, self.SCALING_KEYS))
+    if lc.heads % lc.kv_heads:
+      raise ConfigError(f"{lw}.heads={lc.heads} must be a multiple of kv_heads={lc.kv_heads}")
+    if lc.rot.dims > lc.dim:
+      raise ConfigError(f"{lw}.rot.dims={lc.rot.dims} is more than dim={lc.dim}")
+    if lc.rot.scaling is not None and not lc.rot.scaling["high"] > lc.rot.scaling["low"]:
+      raise ConfigError(f"{lw}.rot.scaling.high must be more than low, got {lc.rot.scaling!r}")
+    decay = right.get("decay")
+    heads = _positive_int(right, "heads", rw)
+    if not isinstance(decay, list) or len(decay) != heads or not all(isinstance(d, (int, float)) and not isinstance(d, bool) and 0 <= d <= 1 for d in decay):
+      raise ConfigError(f"{rw}.decay must list one factor in 0..1 for each of the {heads} heads, got {decay!r}")
+    rc = RetentionConfig(heads, _positive_int(right, "dim", rw), _positive_int(right, "vdim", rw), [float(d) for d in decay],
+                         RotationConfig.read(right, rw, self.SCALING_KEYS))
+    if rc.rot.dims > rc.dim:
+      raise ConfigError(f"{rw}.rot.dims={rc.rot.dims} is more than dim={rc.dim}")
+    return lc, rc, _number(m, "left_scale", where, positive=False), _number(m, "right_scale", where, positive=False)
+
+  def ff_of(self, i: int) -> Optional[int]:
+    """The width of layer ``i``'s dense feed-forward, or None for a layer without one."""
+    mlp = self.layers[i].get("mlp")
+    if mlp is None:
+      return None
+    if not isinstance(mlp, dict) or mlp.get("kind") != "dense":
+      raise ConfigError(f"layers[{i}].mlp.kind={mlp.get('kind') if isinstance(mlp, dict) else mlp!r} is not known (dense)")
+    return _positive_int(mlp, "ff", f"layers[{i}].mlp")
+
+  def low_rank(self, i: int, default: int = 16) -> int:
+    return int((self.low_ranks or {}).get(f"l{i}.decay", default))
+
+  def read_tensor_shapes(self, shapes: Dict[str, tuple]) -> None:
+    ranks = dict(self.low_ranks or {})
+    for i in range(len(self.layers)):
+      shape = shapes.get(f"l{i}.mix.a1")
+      if self.type_of(i) == "gla" and shape is not None and len(shape) == 2:
+        ranks[f"l{i}.decay"] = int(shape[0])
+    self.low_ranks = ranks or None
+
+  def to_dict(self) -> Dict[str, Any]:
+    d = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width, "norm": dict(self.norm),
+         "layers": [dict(x) for x in self.layers]}
+    if self.streams is not None:
+      d["streams"] = self.streams
     if self.low_ranks:
       d["low_ranks"] = dict(self.low_ranks)
     d.update(self.extra)

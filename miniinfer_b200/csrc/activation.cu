@@ -1,4 +1,4 @@
-// SwiGLU activation: out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu in float32, one rounding
+// Activations of the feed-forwards.  SwiGLU: out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu in float32, one rounding
 // (bfloat16: with the hardware's exponential and reciprocal; float32: exact division and expf).
 // Stands where the reference runs a Triton kernel (kernels/triton/silu_mul.py:6-42).
 #include "common.cuh"
@@ -39,7 +39,55 @@ __global__ void silu_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __
   }
 }
 
+// out[i] = max(x[i], 0)^2, squared in float32 and rounded once; out may be x.
+template <typename T>
+__global__ void relu_squared_kernel(T* __restrict__ out, const T* __restrict__ x, size_t total) {
+  mi::grid_dependency_sync();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const float v = fmaxf(mi::to_float(x[idx]), 0.f);
+    out[idx] = mi::from_float<T>(v * v);
+  }
+}
+
+__global__ void relu_squared_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x, size_t total8) {
+  mi::grid_dependency_sync();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
+    const uint4 g = *reinterpret_cast<const uint4*>(x + idx * 8);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
+    uint4 r;
+    __nv_bfloat162* rp = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 a = __bfloat1622float2(gp[k]);
+      a.x = fmaxf(a.x, 0.f); a.y = fmaxf(a.y, 0.f);
+      rp[k] = __floats2bfloat162_rn(a.x * a.x, a.y * a.y);
+    }
+    *reinterpret_cast<uint4*>(out + idx * 8) = r;
+  }
+}
+
 }  // namespace
+
+// Squared ReLU over n values, in place if out == x.
+MI_API int mi_relu_squared(void* out, const void* x, int dtype, long long n, cudaStream_t stream) {
+  MI_REQUIRE(n >= 0, "relu_squared: bad size %lld", n);
+  if (n == 0) return 0;
+  const size_t total = (size_t)n;
+  const int threads = 256;
+  const size_t most = (size_t)mi::sm_count() * 16;
+  if (dtype == MI_BF16 && total % 8 == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)x % 16) == 0) {
+    const size_t total8 = total / 8, want = (total8 + threads - 1) / threads;
+    mi::launch(relu_squared_bf16x8_kernel, dim3((unsigned)(want < most ? want : most)), dim3(threads), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, total8);
+  } else {
+    const size_t want = (total + threads - 1) / threads;
+    const dim3 grid((unsigned)(want < most ? want : most));
+    if (dtype == MI_BF16) mi::launch(relu_squared_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, total);
+    else if (dtype == MI_F32) mi::launch(relu_squared_kernel<float>, grid, dim3(threads), 0, stream, (float*)out, (const float*)x, total);
+    else return mi_fail("relu_squared: unknown dtype %d", dtype);
+  }
+  MI_LAUNCH_OK("relu_squared");
+  return 0;
+}
 
 MI_API int mi_silu_mul(void* out, const void* gu, int dtype, int T, int I, cudaStream_t stream) {
   MI_REQUIRE(T >= 0 && I > 0, "silu_mul: bad sizes T=%d I=%d", T, I);

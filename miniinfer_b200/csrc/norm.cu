@@ -217,6 +217,30 @@ MI_API int mi_add_rmsnorm_pair(void* out1, void* out2, int out_dtype, float* res
   return 0;
 }
 
+namespace {
+template <typename T>
+__global__ void scaled_pair_sum_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b, size_t n, float sa, float sb) {
+  mi::grid_dependency_sync();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = mi::from_float<T>(fmaf(sa, mi::to_float(a[i]), sb * mi::to_float(b[i])));
+}
+}  // namespace
+
+// out = sa * a + sb * b over n values, float32 arithmetic, one rounding (two mixers side by side, summed with constants).
+MI_API int mi_scaled_pair_sum(void* out, const void* a, const void* b, int dtype, long long n, float sa, float sb, cudaStream_t stream) {
+  MI_REQUIRE(n >= 0, "scaled_pair_sum: bad size %lld", n);
+  if (n == 0) return 0;
+  const size_t want = ((size_t)n + 255) / 256, most = (size_t)mi::sm_count() * 16;
+  const dim3 grid((unsigned)(want < most ? want : most));
+  if (dtype == MI_BF16)
+    mi::launch(scaled_pair_sum_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (size_t)n, sa, sb);
+  else if (dtype == MI_F32)
+    mi::launch(scaled_pair_sum_kernel<float>, grid, dim3(256), 0, stream, (float*)out, (const float*)a, (const float*)b, (size_t)n, sa, sb);
+  else return mi_fail("scaled_pair_sum: unknown dtype %d", dtype);
+  MI_LAUNCH_OK("scaled_pair_sum");
+  return 0;
+}
+
 MI_API int mi_rms_pair_sum(void* out, const void* a, const void* b, int dtype, const float* w1, const float* w2, int R, int H,
                            float eps, float scale, cudaStream_t stream) {
   MI_REQUIRE(R >= 0 && H > 0 && eps > 0.f, "rms_pair_sum: bad sizes R=%d H=%d or eps", R, H);

@@ -2,7 +2,10 @@
 //
 //   * divides each query and key head by its root mean square over the head, x / sqrt(mean(x^2) + eps),
 //     in float32 (optionally times a weight per dimension), and writes the query heads, padded with
-//     zeros to the cache's head size, into a packed buffer [token, head, cache head size];
+//     zeros to the cache's head size, into a packed buffer [token, head, cache head size]; with norm_whole the root
+//     mean square is taken over all query heads of the token at once (and over all its key heads), before they are
+//     split, and the weights have a value per head and dimension; a bias per projection column (float32) may be added
+//     to queries, keys and values first;
 //   * optionally rotates the first rot_dims values of each query and key head, after the norm, by the angles of the
 //     token's position (a table row: cos of rot_dims / 2 angles, then their sines): value i pairs with value
 //     i + rot_dims / 2 (halves) or value 2i with 2i + 1 (interleaved); (u, v) -> (u cos - v sin, v cos + u sin);
@@ -28,10 +31,12 @@ struct PrepArgs {
   int proj_stride, q_off, k_off, v_off;
   int nh, nkv, dim, vdim, hdp;
   T* q_out;               // [tokens, nh * hdp]
-  const float* q_w;       // [dim] or null
-  const float* k_w;       // [dim] or null
+  const float* q_w;       // [dim] ([nh * dim] with norm_whole) or null
+  const float* k_w;       // [dim] ([nkv * dim] with norm_whole) or null
+  const float* bias;      // indexed like the projection's columns (queries, keys, values): added before anything else; or null
   float eps;
   int normalise;          // 0: queries and keys pass unchanged
+  int norm_whole;         // the root mean square runs over all query heads (all key heads) of a token, not a head
   const float* lambda;    // device scalar (v_mode 2)
   T* v_other;             // [tokens, nkv * vdim]: written (v_mode 1) or read (v_mode 2)
   int v_mode;
@@ -61,18 +66,30 @@ qkv_prepare_kernel(PrepArgs<T> a) {
       // a query head or a key head
       const bool is_q = u < a.nh;
       const int h = is_q ? u : u - a.nh;
-      const T* src = row + (is_q ? a.q_off : a.k_off) + (size_t)h * a.dim;
+      const int col0 = (is_q ? a.q_off : a.k_off) + h * a.dim;
+      const T* src = row + col0;
       const float* w = is_q ? a.q_w : a.k_w;
+      if (w && a.norm_whole) w += (size_t)h * a.dim;
+      const float* bs = a.bias ? a.bias + col0 : nullptr;
       float v[PREP_MAX_PER_LANE];
       float ss = 0.f;
 #pragma unroll
       for (int i = 0; i < PREP_MAX_PER_LANE; ++i) {
         const int d = lane + 32 * i;
-        v[i] = d < a.dim ? mi::to_float(src[d]) : 0.f;
+        v[i] = d < a.dim ? mi::to_float(src[d]) + (bs ? bs[d] : 0.f) : 0.f;
         ss += v[i] * v[i];
       }
       float r = 1.f;
-      if (a.normalise) r = 1.f / sqrtf(mi::warp_sum(ss) / (float)a.dim + a.eps);
+      if (a.normalise && a.norm_whole) {
+        // every warp of the token's queries (keys) adds up the same squares in the same order
+        const int n = (is_q ? a.nh : a.nkv) * a.dim, c0 = is_q ? a.q_off : a.k_off;
+        float sw = 0.f;
+        for (int d = lane; d < n; d += 32) {
+          const float x = mi::to_float(row[c0 + d]) + (a.bias ? a.bias[c0 + d] : 0.f);
+          sw = fmaf(x, x, sw);
+        }
+        r = 1.f / sqrtf(mi::warp_sum(sw) / (float)n + a.eps);
+      } else if (a.normalise) r = 1.f / sqrtf(mi::warp_sum(ss) / (float)a.dim + a.eps);
       T* dst = nullptr;
       if (is_q) dst = a.q_out + ((size_t)tkn * a.nh + h) * a.hdp;
       else if (slot >= 0) dst = a.kv_layer + ((((size_t)page * 2 + 0) * a.nkv + h) * a.page_size + off) * a.hdp;
@@ -124,6 +141,7 @@ qkv_prepare_kernel(PrepArgs<T> a) {
       // a value head
       const int h = u - a.nh - a.nkv;
       const T* src = row + a.v_off + (size_t)h * a.vdim;
+      const float* bs = a.bias ? a.bias + a.v_off + h * a.vdim : nullptr;
       T* other = a.v_other ? a.v_other + ((size_t)tkn * a.nkv + h) * a.vdim : nullptr;
       T* dst = slot >= 0 ? a.kv_layer + ((((size_t)page * 2 + 1) * a.nkv + h) * a.page_size + off) * a.hdp : nullptr;
 #pragma unroll
@@ -132,7 +150,7 @@ qkv_prepare_kernel(PrepArgs<T> a) {
         if (d >= a.hdp) continue;
         float y = 0.f;
         if (d < a.vdim) {
-          y = mi::to_float(src[d]);
+          y = mi::to_float(src[d]) + (bs ? bs[d] : 0.f);
           if (a.v_mode == 1) other[d] = mi::from_float<T>(y);
           else if (a.v_mode == 2) y = (1.f - lam) * y + lam * mi::to_float(other[d]);
         }
@@ -228,7 +246,7 @@ MI_API int mi_qkv_norm_mix_store(const void* proj, int dtype, int proj_stride, i
                                  int nkv, int dim, int vdim, int hdp, void* q_out, const float* q_w, const float* k_w,
                                  float eps, int normalise, const float* lambda, void* v_other, int v_mode,
                                  const int* slot_mapping, void* kv_layer, int page_size, const float* rope, const int* positions,
-                                 int rot_dims, int interleaved, cudaStream_t stream) {
+                                 int rot_dims, int interleaved, const float* bias, int norm_whole, cudaStream_t stream) {
   MI_REQUIRE(rope == nullptr || (positions != nullptr && rot_dims > 0 && rot_dims % 2 == 0 && rot_dims <= dim),
              "qkv_prepare: a rotation needs positions and an even number of rotated values, at most dim=%d (got %d)", dim, rot_dims);
   MI_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && dim > 0 && vdim > 0 && nh + 2 * nkv <= 4 * 65535, "qkv_prepare: bad sizes");
@@ -239,7 +257,7 @@ MI_API int mi_qkv_norm_mix_store(const void* proj, int dtype, int proj_stride, i
   MI_REQUIRE(slot_mapping == nullptr || (kv_layer != nullptr && page_size > 0), "qkv_prepare: a store needs the cache layer");
   if (T == 0) return 0;
   const size_t es = dtype == MI_BF16 ? 2 : 4;
-  const bool pairs = rope == nullptr && dim % 2 == 0 && vdim % 2 == 0 && hdp % 2 == 0 && proj_stride % 2 == 0 && q_off % 2 == 0 && k_off % 2 == 0 && v_off % 2 == 0 &&
+  const bool pairs = rope == nullptr && bias == nullptr && !norm_whole && dim % 2 == 0 && vdim % 2 == 0 && hdp % 2 == 0 && proj_stride % 2 == 0 && q_off % 2 == 0 && k_off % 2 == 0 && v_off % 2 == 0 &&
                      ((uintptr_t)proj % (2 * es)) == 0 && ((uintptr_t)q_out % (2 * es)) == 0 && ((uintptr_t)kv_layer % (2 * es)) == 0 &&
                      ((uintptr_t)v_other % (2 * es)) == 0;
 #define MI_PREP(TT)                                                                                          \
@@ -250,6 +268,7 @@ MI_API int mi_qkv_norm_mix_store(const void* proj, int dtype, int proj_stride, i
     a.eps = eps; a.normalise = normalise; a.lambda = lambda; a.v_other = (TT*)v_other; a.v_mode = v_mode;     \
     a.slot_mapping = slot_mapping; a.kv_layer = (TT*)kv_layer; a.page_size = page_size;                      \
     a.rope = rope; a.positions = positions; a.rot_dims = rot_dims; a.interleaved = interleaved;              \
+    a.bias = bias; a.norm_whole = norm_whole;                                                                \
     if (pairs) mi::launch(qkv_prepare_pairs_kernel<TT>, dim3(T, (nh + 2 * nkv + PREP_WARPS - 1) / PREP_WARPS), dim3(PREP_WARPS * 32), 0, stream, a); \
     else mi::launch(qkv_prepare_kernel<TT>, dim3(T, (nh + 2 * nkv + PREP_WARPS - 1) / PREP_WARPS), dim3(PREP_WARPS * 32), 0, stream, a);                        \
   } while (0)

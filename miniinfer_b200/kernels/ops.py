@@ -122,14 +122,15 @@ def _stream() -> ctypes.c_void_p:
 # --------------------------------------------------------------------------------------------
 
 
-def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0) -> None:
-  """out[t] = scale * table[ids[t]] as float32.  ids: int32, already checked to lie in the vocabulary."""
+def embedding(out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0, copies: int = 1) -> None:
+  """out[t] = scale * table[ids[t]] as float32, ``copies`` times side by side in a row of out.  ids: int32, already
+  checked to lie in the vocabulary."""
   lib = common_lib()
-  T, H = out.shape
-  if table.shape[1] != H or ids.shape[0] != T:
+  T, H = out.shape[0], table.shape[1]
+  if out.shape[1] != H * copies or ids.shape[0] != T or copies < 1:
     raise KernelError("embedding: shapes do not match")
   _check(lib, lib.mi_embedding(_ptr(out, torch.float32), _ptr(table), _dt(table), _ptr(ids, torch.int32),
-                               T, H, ctypes.c_float(scale), _stream()))
+                               T, H, ctypes.c_float(scale), int(copies), _stream()))
 
 
 def add_layernorm(out: torch.Tensor, resid: torch.Tensor, delta: Optional[torch.Tensor], delta2: Optional[torch.Tensor],
@@ -401,7 +402,7 @@ def qkv_norm_mix_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q
                        mix: Optional[torch.Tensor] = None, v_other: Optional[torch.Tensor] = None, v_mode: int = 0,
                        slot_mapping: Optional[torch.Tensor] = None, kv_layer: Optional[torch.Tensor] = None,
                        rope: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None,
-                       interleaved: bool = False) -> None:
+                       interleaved: bool = False, bias: Optional[torch.Tensor] = None, norm_whole: bool = False) -> None:
   """From the rows of a fused projection (queries at column ``q_off``, keys at ``k_off``, values at ``v_off``) to what
   attention reads, for heads that are not rotated: query and key heads divided by their root mean square over
   ``dim`` (x / sqrt(mean(x^2) + eps), float32; times ``q_weight`` / ``k_weight`` if given); queries into
@@ -410,10 +411,18 @@ def qkv_norm_mix_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q
   (``v_mode`` 1) or left alone (0); keys and values stored into the layer's pages at ``slot_mapping``.
   ``rope [positions, rot_dims]`` float32 (cos of rot_dims / 2 angles, then their sines): the first ``rot_dims`` values of
   every query and key head are rotated, after the norm, by the angles of the token's position - value i with value
-  i + rot_dims / 2, or 2i with 2i + 1 if ``interleaved``.  ``v_off == k_off`` makes the values the keys as projected."""
+  i + rot_dims / 2, or 2i with 2i + 1 if ``interleaved``.  ``v_off == k_off`` makes the values the keys as projected.
+  ``bias`` float32, indexed like the projection's columns and covering the queries, keys and values, is added first.  ``norm_whole``: the root
+  mean square runs over all query heads of a token at once (and over all its key heads), and ``q_weight`` / ``k_weight``
+  hold a value per head and dimension (``[heads * dim]``, ``[kv heads * dim]``)."""
   lib = common_lib()
   T = proj.shape[0]
   hdp = q_out.shape[1] // num_heads
+  if bias is not None and (bias.dim() != 1 or bias.shape[0] < max(q_off + num_heads * dim, k_off + num_kv_heads * dim, v_off + num_kv_heads * vdim)):
+    raise KernelError("qkv_norm_mix_store: the bias must have a value for every query, key and value column of the projection")
+  for wt, n in ((q_weight, num_heads), (k_weight, num_kv_heads)):
+    if wt is not None and wt.shape != ((n * dim,) if norm_whole else (dim,)):
+      raise KernelError("qkv_norm_mix_store: a norm weight does not match the span of its norm")
   if q_out.shape != (T, num_heads * hdp) or q_out.dtype != proj.dtype:
     raise KernelError("qkv_norm_mix_store: q_out does not match the projection rows")
   width = proj.shape[1]
@@ -435,7 +444,8 @@ def qkv_norm_mix_store(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q
     _ptr(slot_mapping, torch.int32) if (slot_mapping is not None and kv_layer is not None) else none,
     _ptr(kv_layer) if kv_layer is not None else none, page_size,
     _ptr(rope, torch.float32) if rope is not None else none, _ptr(positions, torch.int32) if rope is not None else none,
-    int(rope.shape[1]) if rope is not None else 0, int(bool(interleaved)), _stream()))
+    int(rope.shape[1]) if rope is not None else 0, int(bool(interleaved)),
+    _ptr(bias, torch.float32) if bias is not None else none, int(bool(norm_whole)), _stream()))
 
 
 def add_rmsnorm_pair(out1: torch.Tensor, out2: Optional[torch.Tensor], resid: torch.Tensor, delta: Optional[torch.Tensor],
@@ -614,6 +624,111 @@ def gated_delta(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Te
                                  _ptr(ctx.q_len, torch.int32), _ptr(ctx.seq_slot, torch.int32), T, ctx.num_items, heads, kv_heads, dim, vdim,
                                  _ptr(scratch, torch.float32), _ptr(segments, torch.float32) if segments is not None else _ptr(None),
                                  _stream()), kernels=launches)
+
+
+LINEAR_SEGMENTED_MAX_ITEMS = 8     # steps of at most this many requests run long bfloat16 portions in stretches side by side
+LINEAR_SEGMENTED_MAX_BLOCKS = 148  # ... and only while the walk in order would leave SMs idle (blocks in order, all requests)
+
+
+def linear_attention(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: torch.Tensor, state: torch.Tensor, ctx,
+                     heads: int, dim: int, vdim: int, eps: float, decay_logits: Optional[torch.Tensor] = None,
+                     decay_bias: Optional[torch.Tensor] = None, tau: float = 1.0, head_decay: Optional[torch.Tensor] = None,
+                     rope: Optional[torch.Tensor] = None, q_scale: float = 1.0, k_scale: float = 1.0,
+                     norm_weight: Optional[torch.Tensor] = None, gate_silu: bool = True, workspace=None) -> None:
+  """Linear attention with a decaying state over each item's new tokens, from and to the per-request state
+  ``[slots, >= heads * dim * vdim]`` float32: per head ``S <- diag(alpha) S + k v^T; o = S^T q`` with
+  ``alpha = exp(logsigmoid(decay_logits + decay_bias) / tau)`` per token and key channel (``decay_logits [T, heads * dim]``
+  float32) or the constant ``head_decay[h]`` (float32 ``[heads]``); ``out = o / rms(o) * norm_weight * act(gate)``, ``act`` =
+  silu or sigmoid, ``norm_weight [vdim]`` optional.  ``q``, ``k`` ``[T, heads * dim]`` are first rotated by the token's position
+  (``rope [positions, rot_dims]``, cos then sin; value i with value i + rot_dims / 2) and scaled.  ``q``, ``k``, ``v``, ``gate``
+  and ``out`` may be column ranges of wider rows.  Three launches; a bfloat16 step of long prompt portions walks each
+  request's tokens in stretches side by side (five launches), a float32 step always in order."""
+  lib = common_lib()
+  T = v.shape[0]
+  if (q.shape != (T, heads * dim) or k.shape != q.shape or v.shape != (T, heads * vdim) or gate.shape != v.shape or out.shape != v.shape
+      or (norm_weight is not None and norm_weight.shape != (vdim,))):
+    raise KernelError("linear_attention: shapes do not match")
+  if len({t.dtype for t in (out, q, k, v, gate)}) != 1:
+    raise KernelError("linear_attention: the activations differ in dtype")
+  if (decay_logits is None) == (head_decay is None):
+    raise KernelError("linear_attention: give the decays' logits or the heads' constants, one of the two")
+  if decay_logits is not None and (decay_logits.shape != (T, heads * dim) or decay_logits.dtype != torch.float32
+                                   or (decay_bias is not None and decay_bias.shape != (heads * dim,))):
+    raise KernelError("linear_attention: the decays' logits must be float32 [tokens, heads * dim], their bias [heads * dim]")
+  if head_decay is not None and head_decay.shape != (heads,):
+    raise KernelError("linear_attention: one constant decay a head")
+  if state.dim() != 2 or state.stride(1) != 1 or state.dtype != torch.float32:
+    raise KernelError("linear_attention: the state must be float32 rows, one per request slot")
+  (op, ldo), (qp, ldq), (kp, ldk), (vp, ldv), (gp, ldg) = (_cols(t, "linear_attention") for t in (out, q, k, v, gate))
+  ap, lda = _cols(decay_logits, "linear_attention") if decay_logits is not None else (_ptr(None), 0)
+  channel = decay_logits is not None
+  lib.mi_linear_attention_scratch_floats.restype = ctypes.c_longlong
+  n = int(lib.mi_linear_attention_scratch_floats(T, heads, dim, vdim, int(channel))) + 8
+  scratch = workspace.buffer("linear_attention_scratch", (n,), torch.float32) if workspace is not None else \
+    torch.empty(n, dtype=torch.float32, device=v.device)
+  segments, launches = None, 3
+  if (v.dtype == torch.bfloat16 and ctx.num_items <= LINEAR_SEGMENTED_MAX_ITEMS and T >= SCAN_SEGMENTED_MIN_TOKENS * ctx.num_items
+      and ctx.num_items * int(lib.mi_linear_attention_blocks(heads, dim, vdim)) <= LINEAR_SEGMENTED_MAX_BLOCKS
+      and os.environ.get("MINIINFER_B200_LINEAR_SEGMENTS", "1") != "0"):
+    m = ctx.num_items * int(lib.mi_linear_attention_segments()) * heads * dim * (vdim + 1)
+    segments = workspace.buffer("linear_attention_segments", (m,), torch.float32) if workspace is not None else \
+      torch.empty(m, dtype=torch.float32, device=v.device)
+    launches = 5
+  none = _ptr(None)
+  _check(lib, lib.mi_linear_attention(
+    op, ldo, qp, ldq, kp, ldk, vp, ldv, gp, ldg, _dt(v), ap, lda,
+    _ptr(decay_bias, torch.float32) if (channel and decay_bias is not None) else none, ctypes.c_float(1.0 / tau),
+    _ptr(head_decay, torch.float32) if head_decay is not None else none,
+    _ptr(rope, torch.float32) if rope is not None else none, _ptr(ctx.positions, torch.int32) if rope is not None else none,
+    int(rope.shape[1]) if rope is not None else 0, ctypes.c_float(q_scale), ctypes.c_float(k_scale),
+    _ptr(norm_weight, torch.float32) if norm_weight is not None else none, ctypes.c_float(eps), int(bool(gate_silu)),
+    ctypes.c_void_p(state.data_ptr()), ctypes.c_longlong(state.stride(0)), _ptr(ctx.q_start, torch.int32), _ptr(ctx.q_len, torch.int32),
+    _ptr(ctx.seq_slot, torch.int32), T, ctx.num_items, heads, dim, vdim, _ptr(scratch, torch.float32),
+    _ptr(segments, torch.float32) if segments is not None else none, _stream()), kernels=launches)
+
+
+def hyper_connection(res: torch.Tensor, streams: torch.Tensor, y: Optional[torch.Tensor], mix: Optional[torch.Tensor],
+                     out_w: Optional[torch.Tensor], in_w: Optional[torch.Tensor], norm_weight: Optional[torch.Tensor], eps: float,
+                     rows: Optional[torch.Tensor] = None, write_back: bool = True) -> None:
+  """One pass over residual streams ``[tokens, S * width]`` float32 (stream after stream in a row).  With ``y [tokens, width]``
+  the streams are first brought up to date, all at once from the old ones: ``x_t <- sum_s mix[s, t] x_s + out_w[t] y`` (written
+  back if ``write_back``).  Then ``u = sum_t in_w[t] x_t`` (``in_w`` None: the plain sum) and ``res = norm_weight * u / sqrt(mean(u^2)
+  + eps)``, or ``res = u`` without ``norm_weight``.  ``rows`` selects rows of the streams (``res`` has one row per selected row).
+  All float32; ``res`` is rounded once to its dtype."""
+  lib = common_lib()
+  R, W = res.shape
+  if streams.dim() != 2 or streams.shape[1] % W or streams.dtype != torch.float32:
+    raise KernelError("hyper_connection: the streams must be float32 rows of a whole number of streams")
+  S = streams.shape[1] // W
+  if (rows is None and streams.shape[0] != R) or (rows is not None and rows.shape[0] != R):
+    raise KernelError("hyper_connection: res, rows and the streams differ in rows")
+  if y is not None and (y.shape != (streams.shape[0], W) or mix is None or out_w is None or mix.shape != (S, S) or out_w.shape != (S,)):
+    raise KernelError("hyper_connection: an update needs y [tokens, width], mix [S, S] and out [S]")
+  if (in_w is not None and in_w.shape != (S,)) or (norm_weight is not None and norm_weight.shape != (W,)):
+    raise KernelError("hyper_connection: the read weights do not match")
+  none = _ptr(None)
+  _check(lib, lib.mi_hyper_connection(
+    _ptr(res), _dt(res), _ptr(streams, torch.float32), _ptr(y) if y is not None else none, _dt(y) if y is not None else F32,
+    _ptr(mix, torch.float32) if y is not None else none, _ptr(out_w, torch.float32) if y is not None else none,
+    _ptr(in_w, torch.float32) if in_w is not None else none, _ptr(norm_weight, torch.float32) if norm_weight is not None else none,
+    _ptr(rows, torch.int32) if rows is not None else none, R, S, W, ctypes.c_float(eps), int(bool(write_back)), _stream()))
+
+
+def relu_squared(out: torch.Tensor, x: torch.Tensor) -> None:
+  """out = max(x, 0)^2 element by element, squared in float32 and rounded once; ``out`` may be ``x``."""
+  lib = common_lib()
+  if out.shape != x.shape or out.dtype != x.dtype:
+    raise KernelError("relu_squared: out and x differ")
+  _check(lib, lib.mi_relu_squared(_ptr(out), _ptr(x), _dt(x), ctypes.c_longlong(x.numel()), _stream()))
+
+
+def scaled_pair_sum(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor, scale_a: float, scale_b: float) -> None:
+  """out = scale_a * a + scale_b * b element by element, in float32, rounded once."""
+  lib = common_lib()
+  if a.shape != out.shape or b.shape != out.shape or a.dtype != out.dtype or b.dtype != out.dtype:
+    raise KernelError("scaled_pair_sum: shapes or dtypes do not match")
+  _check(lib, lib.mi_scaled_pair_sum(_ptr(out), _ptr(a), _ptr(b), _dt(out), ctypes.c_longlong(out.numel()),
+                                     ctypes.c_float(scale_a), ctypes.c_float(scale_b), _stream()))
 
 
 def latent_down(down: torch.Tensor, q_off: int, kv_off: int, q_rank: int, kv_rank: int, rot_dim: int, q_weight: torch.Tensor,

@@ -36,6 +36,9 @@ class ModelSpec:
   run_list: Optional[List[LayerRun]] = None
   # file tensors that may be present without being loaded, each equal to another file tensor
   aliases: Dict[str, str] = field(default_factory=dict)
+  # file tensors that may be present although this model's parts read none of them (the tensors of a sublayer that the
+  # configuration switches off)
+  unused: List[str] = field(default_factory=list)
   init_std: float = 0.02
 
   def __post_init__(self):

@@ -2,12 +2,14 @@ from .base import (Block, Embedding, FeedForward, Head, HostStep, Mixer, Norm, P
                    StepWork, whole)
 from .block import ParallelBlock, PreNormBlock
 from .embedding import LMHead, TokenEmbedding
-from .feedforward import RoutedExpertsFeedForward, SwiGLUFeedForward
+from .feedforward import ActivatedFeedForward, RoutedExpertsFeedForward, SwiGLUFeedForward
 from .gated_attention import GatedAttentionMixer
+from .hyper import HyperConnectionBlock, StreamSumNorm
 from .latent_attention import LatentAttentionMixer
+from .linear_attention import LinearAttentionMixer
 from .mixer import AttentionMixer
 from .norm import LayerNorm, RMSNorm
-from .position import RotaryEncoding, ScaledRotaryEncoding
+from .position import BandScaledRotaryEncoding, RotaryEncoding, ScaledRotaryEncoding
 from .recurrent import GatedDeltaMixer, SelectiveScanMixer
 from .side_by_side import SideBySideMixer
 from .registry import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, make, register_block,
@@ -19,11 +21,16 @@ register_mixer("latent_attention")(LatentAttentionMixer)
 register_mixer("selective_scan")(SelectiveScanMixer)
 register_mixer("gated_delta")(GatedDeltaMixer)
 register_mixer("side_by_side")(SideBySideMixer)
+register_mixer("linear_attention")(LinearAttentionMixer)
 register_feed_forward("swiglu")(SwiGLUFeedForward)
 register_feed_forward("routed_experts")(RoutedExpertsFeedForward)
+register_feed_forward("activated")(ActivatedFeedForward)
 register_norm("rmsnorm")(RMSNorm)
 register_norm("layernorm")(LayerNorm)
+register_norm("stream_sum_rmsnorm")(StreamSumNorm)
 register_position_encoding("rotary")(RotaryEncoding)
 register_position_encoding("scaled_rotary")(ScaledRotaryEncoding)
+register_position_encoding("band_scaled_rotary")(BandScaledRotaryEncoding)
 register_block("pre_norm")(PreNormBlock)
 register_block("parallel")(ParallelBlock)
+register_block("hyper_connection")(HyperConnectionBlock)

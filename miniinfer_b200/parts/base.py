@@ -52,7 +52,7 @@ class ParamSpec:
   shape: Tuple[int, ...]
   role: str
   sources: List[List[Piece]]
-  init: str = "normal"            # random-weights mode: "normal" (std given by the model), "ones_noise" (about 1), "half_noise" (about 0.5) or "fan_in" (1.5 / sqrt(columns))
+  init: str = "normal"            # random-weights mode: "normal" (std given by the model), "ones_noise" (about 1), "half_noise" (about 0.5), "fan_in" (1.5 / sqrt(columns)), "mean_noise" (about 1 / entries), "identity_noise" (a square matrix about the identity) or "decay_bias" (about 3)
 
   def __post_init__(self):
     if self.role not in ("matrix", "table", "vector", "int"):

@@ -16,15 +16,19 @@ from .base import Block, FeedForward, Mixer, Norm, Part
 
 
 class PreNormBlock(Block):
-  def __init__(self, name: str, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward):
+  """``ffn`` (and its norm) may be None: a layer of a mixer alone, whose output is left pending."""
+
+  def __init__(self, name: str, mixer_norm: Norm, mixer: Mixer, ffn_norm: Optional[Norm], ffn: Optional[FeedForward]):
     super().__init__(name)
+    if ffn is not None and ffn_norm is None:
+      raise ValueError(f"{name}: a feed-forward needs its norm")
     self.mixer_norm = mixer_norm
     self.mixer = mixer
-    self.ffn_norm = ffn_norm
+    self.ffn_norm = ffn_norm if ffn is not None else None
     self.ffn = ffn
 
   def sub_parts(self) -> List[Part]:
-    return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+    return [self.mixer_norm, self.mixer] + ([self.ffn_norm, self.ffn] if self.ffn is not None else [])
 
   def mixer_part(self) -> Optional[Mixer]:
     return self.mixer
@@ -38,6 +42,8 @@ class PreNormBlock(Block):
     else:
       x = self.mixer_norm.add_norm(resid, pending, ctx)
       a = self.mixer.forward(x, ctx, cache)
+    if self.ffn is None:
+      return a
     if a is None and self.ffn.takes_residual(self.ffn_norm, ctx):
       self.ffn.forward_on_residual(resid, self.ffn_norm, ctx)
       return None

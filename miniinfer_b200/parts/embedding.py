@@ -19,22 +19,28 @@ from .base import Embedding, Head, ParamSpec, whole
 
 class TokenEmbedding(Embedding):
   """``scale``: a constant the looked-up row is multiplied with (1: none).  ``tensor``: the table's name in the weights
-  file (default ``<name>.weight``)."""
+  file (default ``<name>.weight``).  ``copies``: the row is written that many times side by side, for models whose
+  residual stream is several streams that start equal."""
 
-  def __init__(self, name: str, vocab_size: int, hidden_size: int, scale: float = 1.0, tensor: Optional[str] = None):
+  def __init__(self, name: str, vocab_size: int, hidden_size: int, scale: float = 1.0, tensor: Optional[str] = None, copies: int = 1):
     super().__init__(name)
+    if copies < 1:
+      raise ValueError(f"{name}: copies must be positive, got {copies}")
     self.vocab_size = vocab_size
     self.hidden_size = hidden_size
     self.scale = float(scale)
     self.tensor = tensor or f"{name}.weight"
+    self.copies = copies
 
   def param_specs(self) -> Dict[str, ParamSpec]:
     shape = (self.vocab_size, self.hidden_size)
     return {"weight": ParamSpec(shape, "table", [whole(self.tensor, shape)])}
 
   def forward(self, ids: torch.Tensor, ctx) -> torch.Tensor:
-    out = ctx.ws.buffer("resid", (ids.shape[0], self.hidden_size), torch.float32)
-    if self.scale == 1.0:
+    out = ctx.ws.buffer("resid", (ids.shape[0], self.copies * self.hidden_size), torch.float32)
+    if self.copies != 1:
+      ops.embedding(out, self.weight, ids, self.scale, self.copies)
+    elif self.scale == 1.0:
       ops.embedding(out, self.weight, ids)
     else:
       ops.embedding(out, self.weight, ids, self.scale)

@@ -61,6 +61,43 @@ class SwiGLUFeedForward(FeedForward):
     return out
 
 
+class ActivatedFeedForward(FeedForward):
+  """Dense feed-forward of two matrices with an activation between them: ``down(act(up(x)))``.  ``activation``:
+  ``relu_squared`` (``max(z, 0)^2``).  ``tensors``: the file names of the up and down matrices after ``<name>.``."""
+
+  ACTIVATIONS = ("relu_squared",)
+
+  def __init__(self, name: str, hidden_size: int, intermediate_size: int, activation: str = "relu_squared",
+               tensors: Tuple[str, str] = ("up", "down")):
+    super().__init__(name)
+    if activation not in self.ACTIVATIONS:
+      raise ValueError(f"{name}: activation {activation!r} is not known ({', '.join(self.ACTIVATIONS)})")
+    self.hidden_size = hidden_size
+    self.intermediate_size = intermediate_size
+    self.activation = activation
+    self.tensors = tuple(tensors)
+
+  def param_specs(self) -> Dict[str, ParamSpec]:
+    H, I = self.hidden_size, self.intermediate_size
+    u, d = (f"{self.name}.{t}" for t in self.tensors)
+    return {"up": ParamSpec((I, H), "matrix", [whole(u, (I, H))]), "down": ParamSpec((H, I), "matrix", [whole(d, (H, I))])}
+
+  def validate(self, dtype: torch.dtype) -> None:
+    if dtype == torch.bfloat16:
+      for what, k in (("hidden_size", self.hidden_size), ("intermediate_size", self.intermediate_size)):
+        if k % 8:
+          raise ValueError(f"{self.name}: {what}={k} must be a multiple of 8 in bfloat16 (rows are read 16 bytes at a time)")
+
+  def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    T = x.shape[0]
+    act = ctx.ws.buffer("ffn_act", (T, self.intermediate_size), ctx.dtype)
+    ops.linear(act, x, self.up)
+    ops.relu_squared(act, act)
+    out = ctx.ws.buffer("ffn_out", (T, self.hidden_size), ctx.dtype)
+    ops.linear(out, act, self.down)
+    return out
+
+
 class RoutedExpertsFeedForward(FeedForward):
   """A mixture of ``num_experts`` small SwiGLU feed-forward layers of which each token uses ``top``.
 

@@ -5,9 +5,11 @@ first tokens that stay visible behind the window - as a mixer part over the page
 For the normalised rows ``h`` of a step, with ``H`` query heads, ``G`` key/value heads (query head ``i`` reads
 key/value head ``i // (H / G)``), query/key size ``dim`` and value size ``vdim``:
 
-  * one fused product gives ``q``, ``k``, ``v`` and the gate's logits ``g`` (no biases);
+  * one fused product gives ``q``, ``k``, ``v`` and the gate's logits ``g``; with ``biases`` a bias each is added to ``q``,
+    ``k`` and ``v`` (float32, file tensors ``q.b``, ``k.b``, ``v.b``);
   * every head of ``q`` and ``k`` is divided by its root mean square, ``x / sqrt(mean(x^2) + eps)`` (float32), and
-    multiplied by a weight per dimension shared by all heads if ``norm_weights``;
+    multiplied by a weight per dimension shared by all heads if ``norm_weights``; with ``norm_over="projection"`` the root
+    mean square runs over the whole of ``q`` (of ``k``) before the heads are split, and the weights have the projection's size;
   * with ``rotary`` (a position encoding that has a table) the first ``rotary_dim`` values of every query and key head are
     then rotated by the token's position, value i with value i + rotary_dim / 2 or, ``rotary_interleaved``, 2i with 2i + 1;
     without it positions do not enter the scores;
@@ -44,12 +46,18 @@ class GatedAttentionMixer(AttentionMixer):
                value_mix: Optional[str] = None, value_mix_key: str = "value_mix_source",
                tensors: Optional[Dict[str, str]] = None, rotary: Optional[PositionEncoding] = None,
                rotary_interleaved: bool = False, norm_weights: bool = False, values_from_keys: bool = False,
-               keep_first: int = 0):
+               keep_first: int = 0, biases: bool = False, norm_over: str = "head"):
     super().__init__(name, hidden_size, num_heads, num_kv_heads, dim, scale, norm_eps, rotary, window)
     if values_from_keys and (vdim != dim or value_mix is not None):
       raise ValueError(f"{name}: values that are the keys have the keys' size ({dim}, got vdim={vdim}) and are not mixed")
     if keep_first < 0 or (keep_first and window is None):
       raise ValueError(f"{name}: keep_first={keep_first} needs a window and must not be negative")
+    if norm_over not in ("head", "projection"):
+      raise ValueError(f"{name}: norm_over must be 'head' or 'projection', got {norm_over!r}")
+    if biases and (values_from_keys or value_mix is not None):
+      raise ValueError(f"{name}: biases go with projected, unmixed values")
+    self.biases = bool(biases)
+    self.norm_whole = norm_over == "projection"
     self.rotary_interleaved = bool(rotary_interleaved)
     self.norm_weights = bool(norm_weights)
     self.values_from_keys = bool(values_from_keys)
@@ -65,7 +73,8 @@ class GatedAttentionMixer(AttentionMixer):
     self.gated = gated
     self.value_mix = value_mix
     self.value_mix_key = value_mix_key
-    t = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "sink": "sink", "mix": "vmix", "q_norm": "q.norm", "k_norm": "k.norm"}
+    t = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "sink": "sink", "mix": "vmix", "q_norm": "q.norm", "k_norm": "k.norm",
+         "q_bias": "q.b", "k_bias": "k.b", "v_bias": "v.b"}
     t.update(tensors or {})
     self.tensors = t
     H, G = num_heads, num_kv_heads
@@ -88,8 +97,14 @@ class GatedAttentionMixer(AttentionMixer):
     specs = {"qkvg": ParamSpec((self.proj_width, Hd), "matrix", [pieces]),
              "o": ParamSpec((Hd, H * Dv), "matrix", [whole(f"{n}.{t['o']}", (Hd, H * Dv))])}
     if self.norm_weights:
-      specs["q_norm"] = ParamSpec((D,), "vector", [whole(f"{n}.{t['q_norm']}", (D,))], init="ones_noise")
-      specs["k_norm"] = ParamSpec((D,), "vector", [whole(f"{n}.{t['k_norm']}", (D,))], init="ones_noise")
+      nq, nk = ((H * D,), (G * D,)) if self.norm_whole else ((D,), (D,))
+      specs["q_norm"] = ParamSpec(nq, "vector", [whole(f"{n}.{t['q_norm']}", nq)], init="ones_noise")
+      specs["k_norm"] = ParamSpec(nk, "vector", [whole(f"{n}.{t['k_norm']}", nk)], init="ones_noise")
+    if self.biases:
+      # one vector over the fused projection's query, key and value columns
+      specs["bias"] = ParamSpec((self.g_off,), "vector", [[
+        Piece(f"{n}.{t['q_bias']}", self.q_off, (H * D,)), Piece(f"{n}.{t['k_bias']}", self.k_off, (G * D,)),
+        Piece(f"{n}.{t['v_bias']}", self.v_off, (G * Dv,))]], init="half_noise")
     if self.sinks:
       specs["sink"] = ParamSpec((H,), "vector", [whole(f"{n}.{t['sink']}", (H,))])
     if self.value_mix is not None:
@@ -135,7 +150,7 @@ class GatedAttentionMixer(AttentionMixer):
                            self.q_norm if self.norm_weights else None, self.k_norm if self.norm_weights else None, mix, v_other, v_mode,
                            ctx.slot_mapping[cache.group] if cache.writes else None, cache.tensor if cache.writes else None,
                            rope=self.position.rotary_table() if self.position is not None else None, positions=ctx.positions,
-                           interleaved=self.rotary_interleaved)
+                           interleaved=self.rotary_interleaved, bias=self.bias if self.biases else None, norm_whole=self.norm_whole)
     attn = ctx.ws.buffer("attn_out", (T, H * Dv), ctx.dtype)
     ops.attention(attn, q_heads, cache.tensor, ctx.block_tables[cache.group], self._batch(ctx), H, G, hdp, self.scale,
                   self.window, sink=self.sink if self.sinks else None, gate=proj if self.gated else None,

@@ -83,3 +83,37 @@ class ScaledRotaryEncoding(RotaryEncoding):
     f, m = self.frequencies()
     angles = torch.arange(positions, dtype=torch.float64)[:, None] * f[None, :]
     return torch.cat((angles.cos() * m, angles.sin() * m), dim=-1).float().contiguous()
+
+
+class BandScaledRotaryEncoding(RotaryEncoding):
+  """Rotary angles whose low frequencies are divided by ``factor`` and whose high frequencies stay, by wavelength
+  (the scaling of Llama 3.1): with ``f_i = theta^(-2i/dims)`` and wavelength ``l_i = 2 pi / f_i``, ``f_i`` stays where
+  ``l_i < original / high``, becomes ``f_i / factor`` where ``l_i > original / low``, and between the two
+  ``(1 - s) f_i / factor + s f_i`` with ``s = (original / l_i - low) / (high - low)``.  cos and sin are not scaled.  Angles
+  are made in float64 and rounded once.  Without ``scaling`` this is the plain table."""
+
+  def __init__(self, name: str, rotary_dim: int, theta: float, max_position_embeddings: int, scaling: Optional[dict] = None):
+    super().__init__(name, rotary_dim, theta, max_position_embeddings)
+    if scaling is not None:
+      for key in ("factor", "low", "high", "original"):
+        if not isinstance(scaling.get(key), (int, float)) or not scaling[key] > 0:
+          raise ValueError(f"{name}: scaling.{key} must be a positive number, got {scaling.get(key)!r}")
+      if not scaling["high"] > scaling["low"]:
+        raise ValueError(f"{name}: scaling.high must be more than scaling.low")
+    self.scaling = dict(scaling) if scaling is not None else None
+
+  def frequencies(self) -> torch.Tensor:
+    """Frequencies [dims / 2] in float64."""
+    import math
+    dims = self.rotary_dim
+    f = self.theta ** (-2.0 * torch.arange(0, dims // 2, dtype=torch.float64) / dims)
+    s = self.scaling
+    if s is None:
+      return f
+    turns = s["original"] * f / (2 * math.pi)          # original / wavelength
+    blend = ((turns - s["low"]) / (s["high"] - s["low"])).clamp(0.0, 1.0)
+    return (1.0 - blend) * f / s["factor"] + blend * f
+
+  def build_table(self, positions: int) -> torch.Tensor:
+    angles = torch.arange(positions, dtype=torch.float64)[:, None] * self.frequencies()[None, :]
+    return torch.cat((angles.cos(), angles.sin()), dim=-1).float().contiguous()

@@ -117,6 +117,7 @@ def load_weights(spec: ModelSpec, model_dir: str, compute_dtype: torch.dtype, de
           wrong.append(f"{a}: file has {list(index[a][1])}, but it must equal {t} {list(index[t][1])}")
         else:
           alias_checks.append((a, t))
+  used.update(fname(n) for n in spec.unused)
   unexpected = sorted(n for n in index if n not in used)
   if missing or unexpected or wrong:
     raise WeightLoadError(model_dir, sorted(set(missing)), unexpected, wrong)

@@ -30,6 +30,12 @@ def _draw(shape, init: str, std: float, gen: torch.Generator, device="cpu") -> t
     return 1.0 + NORM_NOISE * t
   if init == "half_noise":
     return 0.5 + NORM_NOISE * t
+  if init == "mean_noise":      # weights of a weighted mean over the entries, with noise
+    return 1.0 / max(1, int(shape[-1])) + NORM_NOISE * t
+  if init == "identity_noise":  # a square matrix near the identity
+    return torch.eye(int(shape[-1]), dtype=torch.float32, device=device) + NORM_NOISE * t
+  if init == "decay_bias":      # logits of decays that keep a memory for tens to hundreds of tokens
+    return 3.0 + 2.0 * t
   if init == "fan_in":          # logits of about unit size from rows of about unit size: a router that does choose
     return t * (1.5 / max(1, int(shape[-1])) ** 0.5)
   return std * t
