@@ -243,3 +243,81 @@ def write_model(cfg: dict, W: Dict[str, torch.Tensor], folder: str, dtype: torch
     json.dump(cfg, f)
   save_file({k: v.to(dtype).contiguous() for k, v in W.items()}, os.path.join(folder, "model.safetensors"))
   return folder
+
+
+def make_model_dir(cfg: dict, folder: str, seed: int, ranks: Optional[Dict[int, int]] = None) -> str:
+  return write_model(cfg, make_model(cfg, seed, ranks), folder)
+
+
+def read_weights(model_dir: str) -> Dict[str, torch.Tensor]:
+  from safetensors.torch import load_file
+  return {k: v.float() for k, v in load_file(os.path.join(model_dir, "model.safetensors")).items()}
+
+
+def read_config(model_dir: str) -> dict:
+  with open(os.path.join(model_dir, "config.json"), encoding="utf-8") as f:
+    return json.load(f)
+
+
+def generate(cfg: dict, W: Dict[str, torch.Tensor], prompt: List[int], n: int) -> List[int]:
+  ids = list(prompt)
+  for _ in range(n):
+    ids.append(int(forward(cfg, W, ids)[-1].argmax()))
+  return ids[len(prompt):]
+
+
+# ------------------------------------------------------------------------------------------ configurations
+
+
+def dense(ff) -> dict:
+  return {"kind": "dense", "ff": ff}
+
+
+def gla(heads, dim, vdim, tau, mlp) -> dict:
+  return {"type": "gla", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "tau": tau}, "mlp": mlp}
+
+
+def rot_of(dims, base, scaling=None) -> dict:
+  r = {"dims": dims, "base": base}
+  if scaling is not None:
+    r["scaling"] = scaling
+  return r
+
+
+def pair(left: dict, right: dict, left_scale, right_scale, mlp) -> dict:
+  return {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": left_scale, "right_scale": right_scale}, "mlp": mlp}
+
+
+def left_of(heads, kv_heads, dim, vdim, rot, scale) -> dict:
+  return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "rot": rot, "scale": scale}
+
+
+def right_of(heads, dim, vdim, rot, decay) -> dict:
+  return {"heads": heads, "dim": dim, "vdim": vdim, "rot": rot, "decay": decay}
+
+
+# Three configurations that differ in every size, in the order of their layers and in what is there at all: A has three
+# streams, a layer without a feed-forward, grouped and ungrouped attention heads, rotations over a part of a head with
+# all three bands of the frequency scaling, and odd sizes (a key size that is no multiple of 16, more value than key
+# channels and the reverse); B has no streams (the usual residual sum), starts with a pair, and rotates whole heads
+# without scaling; C has one stream (its hyper-connection weights still act), heads of 64 and 128 values for the
+# tensor-core attention kernels, key sizes past 128 in the linear attention, and decays of 0 and 1.
+CONFIGS = {
+  "A": {"architecture": "Famupel", "vocab": 300, "width": 64, "norm": {"eps": 1e-5}, "streams": 3, "layers": [
+    gla(3, 20, 24, 8.0, dense(96)),
+    pair(left_of(4, 1, 24, 16, rot_of(16, 10000.0, {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}), 0.3),
+         right_of(2, 24, 40, rot_of(8, 5000.0), [0.9, 0.996]), 0.7, 1.3, dense(80)),
+    gla(1, 40, 16, 4.0, None),
+    pair(left_of(2, 2, 16, 32, rot_of(8, 100.0), 0.25), right_of(3, 16, 8, rot_of(16, 300.0), [0.5, 0.97, 0.999]), 1.2, 0.6, None),
+    gla(2, 16, 16, 1.0, dense(72))]},
+  "B": {"architecture": "Famupel", "vocab": 512, "width": 96, "norm": {"eps": 1e-6}, "layers": [
+    pair(left_of(6, 3, 32, 32, rot_of(32, 50000.0), 0.2), right_of(2, 48, 24, rot_of(48, 10000.0), [0.98, 0.9]), 1.0, 1.0, dense(128)),
+    gla(4, 24, 8, 32.0, dense(64)),
+    gla(2, 32, 48, 2.0, None)]},
+  "C": {"architecture": "Famupel", "vocab": 333, "width": 128, "norm": {"eps": 1e-6}, "streams": 1, "layers": [
+    gla(1, 160, 32, 16.0, dense(160)),
+    pair(left_of(4, 2, 64, 128, rot_of(64, 500000.0, {"factor": 2.0, "low": 2.0, "high": 8.0, "original": 128}), 0.125),
+         right_of(2, 64, 64, rot_of(32, 10000.0), [1.0, 0.0]), 0.5, 2.0, dense(96)),
+    pair(left_of(2, 1, 128, 64, rot_of(32, 10000.0), 0.09), right_of(1, 136, 16, rot_of(136, 10000.0), [0.99]), 1.0, 1.0, dense(64))]},
+}
+RANKS = {"A": {0: 8, 2: 4, 4: 16}, "B": {1: 12, 2: 8}, "C": {0: 16}}

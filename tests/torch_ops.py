@@ -17,8 +17,8 @@ from typing import Optional
 import torch
 
 
-def embedding(out, table, ids, scale=1.0):
-  out.copy_(table[ids.long()].float() * scale)
+def embedding(out, table, ids, scale=1.0, copies=1):
+  out.copy_((table[ids.long()].float() * scale).repeat(1, copies))
 
 
 def add_layernorm(out, resid, delta, delta2, weight, bias, eps, rows=None, write_back=True):
@@ -110,21 +110,25 @@ def qk_norm_rope_store(qkv, q_weight, k_weight, cos_sin, positions, slot_mapping
 
 def qkv_norm_mix_store(proj, q_off, k_off, v_off, q_out, num_heads, num_kv_heads, dim, vdim, eps, normalise=True,
                        q_weight=None, k_weight=None, mix=None, v_other=None, v_mode=0, slot_mapping=None, kv_layer=None,
-                       rope=None, positions=None, interleaved=False):
+                       rope=None, positions=None, interleaved=False, bias=None, norm_whole=False):
   T = proj.shape[0]
   H, G = num_heads, num_kv_heads
   hdp = q_out.shape[1] // H
   x = proj.float()
+  if bias is not None:
+    x = x.clone()
+    x[:, :bias.shape[0]] += bias
   q = x[:, q_off:q_off + H * dim].reshape(T, H, dim)
   k = x[:, k_off:k_off + G * dim].reshape(T, G, dim)
   v = x[:, v_off:v_off + G * vdim].reshape(T, G, vdim)
   if normalise:
-    q = q / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + eps)
-    k = k / torch.sqrt(k.pow(2).mean(-1, keepdim=True) + eps)
+    over = (-2, -1) if norm_whole else -1
+    q = q / torch.sqrt(q.pow(2).mean(over, keepdim=True) + eps)
+    k = k / torch.sqrt(k.pow(2).mean(over, keepdim=True) + eps)
   if q_weight is not None:
-    q = q * q_weight
+    q = q * (q_weight.view(H, dim) if norm_whole else q_weight)
   if k_weight is not None:
-    k = k * k_weight
+    k = k * (k_weight.view(G, dim) if norm_whole else k_weight)
   if rope is not None:
     q, k = _rotate(q, rope, positions, interleaved), _rotate(k, rope, positions, interleaved)
   if v_mode == 1:
@@ -327,6 +331,59 @@ def gated_delta(out, q, k, v, a, b, gate, dt_bias, A_log, norm_w, eps, state, ct
     state[slot, :H * D * Dv] = S.reshape(-1)
 
 
+def linear_attention(out, q, k, v, gate, state, ctx, heads, dim, vdim, eps, decay_logits=None, decay_bias=None, tau=1.0,
+                     head_decay=None, rope=None, q_scale=1.0, k_scale=1.0, norm_weight=None, gate_silu=True, workspace=None):
+  H, D, Dv = heads, dim, vdim
+  T = v.shape[0]
+  qf, kf = q.float().reshape(T, H, D), k.float().reshape(T, H, D)
+  if rope is not None:
+    qf, kf = _rotate(qf, rope, ctx.positions, False), _rotate(kf, rope, ctx.positions, False)
+  qf, kf = qf * q_scale, kf * k_scale
+  if decay_logits is not None:
+    z = decay_logits.float() + (decay_bias if decay_bias is not None else 0.0)
+    alpha = torch.exp(torch.nn.functional.logsigmoid(z) / tau).view(T, H, D)
+  else:
+    alpha = head_decay.float()[None, :, None].expand(T, H, D)
+  for row0, n, slot in _items(ctx):
+    S = state[slot, :H * D * Dv].view(H, D, Dv).clone()
+    for t in range(row0, row0 + n):
+      S = alpha[t][:, :, None] * S + kf[t][:, :, None] * v[t].float().view(H, 1, Dv)
+      o = torch.einsum("hdv,hd->hv", S, qf[t])
+      o = o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps)
+      if norm_weight is not None:
+        o = o * norm_weight
+      g = gate[t].float().view(H, Dv)
+      out[t] = (o * (g * torch.sigmoid(g) if gate_silu else torch.sigmoid(g))).reshape(-1).to(out.dtype)
+    state[slot, :H * D * Dv] = S.reshape(-1)
+
+
+def hyper_connection(res, streams, y, mix, out_w, in_w, norm_weight, eps, rows=None, write_back=True):
+  W = res.shape[1]
+  S = streams.shape[1] // W
+  idx = rows.long() if rows is not None else None
+  x = (streams if idx is None else streams[idx]).view(-1, S, W)
+  if y is not None:
+    yy = (y if idx is None else y[idx]).float()
+    x = torch.einsum("st,nsw->ntw", mix, x) + out_w[None, :, None] * yy[:, None, :]
+    if write_back:
+      if idx is None:
+        streams.copy_(x.reshape(-1, S * W))
+      else:
+        streams[idx] = x.reshape(-1, S * W)
+  u = x.sum(1) if in_w is None else torch.einsum("s,nsw->nw", in_w, x)
+  if norm_weight is not None:
+    u = norm_weight * (u / torch.sqrt(u.pow(2).mean(-1, keepdim=True) + eps))
+  res.copy_(u.to(res.dtype))
+
+
+def relu_squared(out, x):
+  out.copy_((torch.relu(x.float()) ** 2).to(out.dtype))
+
+
+def scaled_pair_sum(out, a, b, scale_a, scale_b):
+  out.copy_((scale_a * a.float() + scale_b * b.float()).to(out.dtype))
+
+
 def latent_down(down, q_off, kv_off, q_rank, kv_rank, rot_dim, q_weight, kv_weight, eps, cq_out, rope, positions, interleaved,
                 slot_mapping, kv_layer):
   T = down.shape[0]
@@ -420,5 +477,5 @@ def install(monkeypatch) -> None:
   for name in ("embedding", "add_rmsnorm", "add_layernorm", "linear", "linear_swiglu", "qk_norm_rope_store", "qkv_norm_mix_store",
                "attention", "routed_experts", "silu_mul", "sample", "linear_normed", "linear_swiglu_normed", "linear_add",
                "add_rmsnorm_pair", "rms_pair_sum", "linear_batched", "causal_conv", "selective_scan", "gated_delta", "latent_down",
-               "latent_query"):
+               "latent_query", "linear_attention", "hyper_connection", "relu_squared", "scaled_pair_sum"):
     monkeypatch.setattr(ops, name, globals()[name])
