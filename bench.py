@@ -507,6 +507,33 @@ def kernel_case(name: str, reps: int = 3) -> str:
       out = torch.empty(T, H * Dv, dtype=torch.bfloat16, device=dev)
       fn = lambda: ops.gated_delta(out, q, k, v, a_in, b_in, gate, dt_bias, A_log, norm_w, 1e-6, state, ctx, H, G, Dk, Dv, workspace=ws)
       what = f"{T} tokens ({cuts[0]} of one request), {H} heads of {Dk} x {Dv} on {G} q/k heads"
+  elif name == "linear_attention":
+    # as the delta rule's case: one prompt portion of 8192 tokens beside seven decode tokens, 16 heads of 128 x 128, a decay per
+    # token and key channel (the walk in order: MINIINFER_B200_LINEAR_SEGMENTS=0 in the environment; else stretches side by side)
+    from types import SimpleNamespace
+    cuts = [8192] + [1] * 7
+    T = sum(cuts)
+    it = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    ctx = SimpleNamespace(q_start=it([sum(cuts[:i]) for i in range(len(cuts))]), q_len=it(cuts), seq_slot=it(list(range(len(cuts)))),
+                          num_items=len(cuts), token_item=it([b for b, n in enumerate(cuts) for _ in range(n)]),
+                          positions=it([i for n in cuts for i in range(n)]))
+    H, Dk, Dv = 16, 128, 128
+    q, k, v, gate = rnd(T, H * Dk), rnd(T, H * Dk), rnd(T, H * Dv), rnd(T, H * Dv)
+    logits, bias, norm_w = rnd(T, H * Dk, dtype=torch.float32), rnd(H * Dk, dtype=torch.float32) + 3.0, 1 + 0.1 * rnd(Dv, dtype=torch.float32)
+    state = torch.zeros((len(cuts), H * Dk * Dv), dtype=torch.float32, device=dev)
+    out = torch.empty(T, H * Dv, dtype=torch.bfloat16, device=dev)
+    fn = lambda: ops.linear_attention(out, q, k, v, gate, state, ctx, H, Dk, Dv, 1e-6, decay_logits=logits, decay_bias=bias, tau=16.0,
+                                      q_scale=Dk ** -0.5, norm_weight=norm_w, workspace=ws)
+    what = f"{T} tokens ({cuts[0]} of one request), {H} heads of {Dk} x {Dv}, decays per channel"
+  elif name == "hyper_connection":
+    # the kernel between two sublayers: 16384 rows of 4 streams x 2048 values float32 (537 MB, read and written) and a bfloat16 sublayer output
+    T, S, W = 16384, 4, 2048
+    streams, y = rnd(T, S * W, dtype=torch.float32), rnd(T, W)
+    mix, out_w, in_w = torch.eye(S, device=dev) + 0.1 * rnd(S, S, dtype=torch.float32), rnd(S, dtype=torch.float32), rnd(S, dtype=torch.float32)
+    norm_w = 1 + 0.1 * rnd(W, dtype=torch.float32)
+    res = torch.empty(T, W, dtype=torch.bfloat16, device=dev)
+    fn = lambda: ops.hyper_connection(res, streams, y, mix, out_w, in_w, norm_w, 1e-6)
+    what = f"{T} rows of {S} streams x {W} float32 ({(2 * T * S * W * 4 + 2 * T * W * 2) / 1e6:.0f} MB in and out)"
   else:
     raise SystemExit(f"unknown kernel case {name!r}")
   fn()
@@ -522,7 +549,7 @@ def kernel_case(name: str, reps: int = 3) -> str:
 
 KERNEL_CASES = ("sample", "silu_mul", "gemm_f32", "gemm_tc_plain", "gemm_stream", "attention_generic", "attention_prefill_tc",
                 "attention_prefill_tc_pairs", "attention_prefill_mma", "attention_decode_cpasync", "experts_many_rows", "experts_few_rows",
-                "selective_scan", "delta_rule")
+                "selective_scan", "delta_rule", "linear_attention", "hyper_connection")
 
 
 def mixed_workload(model_dir: str, requests: int = 64, outputs: int = 256) -> dict:
@@ -1015,8 +1042,163 @@ def vugudra_one(name: str, cfg: dict, size: dict, batch: int, steps: int, warmup
   return out
 
 
+# ---------------------------------------------------------------------------------------------- --compare famupel
+# Sizes for the comparison of the Famupel design with the closest design the engine has, Vugudra (attention beside a
+# recurrence with a matrix state a head, recurrent layers between), at equal size: the sizes of the Vugudra comparison and,
+# for Famupel, gated linear attention and retention with the delta rule's heads and state (128 x 128 a head), the
+# attention's heads without a window, a feed-forward of two matrices with the weights of the gated one's three, and
+# residual streams.  The layers go gated linear attention twice, attention beside retention, and again.
+FAMUPEL_SIZES = {
+  "s": dict(VUGUDRA_SIZES["s"], gla=dict(heads=8, dim=128, vdim=128, rank=64, tau=16.0), ret=dict(heads=8, dim=128, vdim=128), streams=2),
+  "m": dict(VUGUDRA_SIZES["m"], gla=dict(heads=16, dim=128, vdim=128, rank=128, tau=16.0), ret=dict(heads=16, dim=128, vdim=128), streams=2),
+  "l": dict(VUGUDRA_SIZES["l"], gla=dict(heads=32, dim=128, vdim=128, rank=128, tau=16.0), ret=dict(heads=32, dim=128, vdim=128), streams=4),
+}
+
+
+def famupel_configs(size: dict) -> dict:
+  W, H, G, hd, L = size["width"], size["heads"], size["kv_heads"], size["head"], size["layers"]
+  gl, rt = size["gla"], size["ret"]
+  mlp = {"kind": "dense", "ff": size["ff"] * 3 // 2}
+  kinds = [
+    {"type": "gla", "mixer": {k: gl[k] for k in ("heads", "dim", "vdim", "tau")}, "mlp": mlp},
+    {"type": "gla", "mixer": {k: gl[k] for k in ("heads", "dim", "vdim", "tau")}, "mlp": mlp},
+    {"type": "parallel", "mlp": mlp,
+     "mixer": {"left": {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                        "rot": {"dims": hd, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
+               "right": {"heads": rt["heads"], "dim": rt["dim"], "vdim": rt["vdim"], "rot": {"dims": rt["dim"], "base": 10000.0},
+                         "decay": [1.0 - 2.0 ** (-5 - 5.0 * i / max(1, rt["heads"] - 1)) for i in range(rt["heads"])]},
+               "left_scale": 1.0, "right_scale": 1.0}},
+  ]
+  layers = [kinds[i % 3] for i in range(L)]
+  fam = {"architecture": "Famupel", "vocab": COMPARE_VOCAB, "width": W, "norm": {"eps": 1e-6}, "streams": size["streams"], "layers": layers,
+         "low_ranks": {f"l{i}.decay": gl["rank"] for i in range(L) if i % 3 != 2}}
+  return {"vugudra": vugudra_configs(size)["vugudra"], "famupel": fam}
+
+
+def _famupel_groups(times: dict) -> dict:
+  import re
+  g = {"attention": 0.0, "dense_products": 0.0, "linear_attention": 0.0, "streams": 0.0, "other": 0.0}
+  for name, us in times.items():
+    if re.search(r"decode_tma_kernel|decode_cluster_kernel|decode_split_kernel|decode_merge|attention_prefill|attention_generic", name):
+      g["attention"] += us
+    elif re.search(r"linear_prepare|linear_recurrence|linear_carry|linear_output", name):
+      g["linear_attention"] += us
+    elif "hyper_connection" in name:
+      g["streams"] += us
+    elif "gemm_skinny" in name or "gemm_tc_kernel" in name or "gemm_stream_tc" in name or \
+        ("anonymous namespace" not in name and re.search(r"nvjet|cutlass|cublas|gemm|gemv|xmma", name, re.I)):
+      g["dense_products"] += us
+    elif not name.startswith("Memcpy") and not name.startswith("Memset"):
+      g["other"] += us
+  return g
+
+
+def famupel_one(name: str, cfg: dict, size: dict, batch: int, steps: int, warmup: int, pk: dict, kernels: bool) -> dict:
+  """Prefill and decode of one model of the comparison; with ``kernels`` the device time of its kinds of kernels and the
+  rates they reach against the measured peaks (run with dependent launch off, see main)."""
+  if name == "vugudra":
+    return vugudra_one(name, cfg, size, batch, steps, warmup, pk, kernels)
+  import torch
+  from miniinfer_b200.engine import StepItem
+  from miniinfer_b200.sampling import Sampler, SamplingParams
+  W, H, G, hd, L = size["width"], size["heads"], size["kv_heads"], size["head"], size["layers"]
+  T = PREFILL_TOKENS
+  with tempfile.TemporaryDirectory() as d:
+    with open(os.path.join(d, "config.json"), "w") as f:
+      json.dump(cfg, f)
+    engine = build_engine(d, batch)
+    if not kernels:
+      dec = time_decode(engine, batch, steps, warmup)
+      pre = time_prefill(engine)
+      out = {"decode_tok_s": round(dec["tok_s"], 1), "decode_ms": round(dec["ms"], 4), "launches_per_decode_step": int(dec["launches_per_step"]),
+             "prefill_tok_s": round(T / (pre["ms"] * 1e-3), 1), "prefill_ms": round(pre["ms"], 3)}
+    else:
+      rids = fill_context(engine, batch, CONTEXT, seed=1000 + batch)
+      params = [SamplingParams(temperature=0.6, max_tokens=GENERATED, ignore_eos=True)] * batch
+      tokens_dev = torch.zeros(max(batch, 1), dtype=torch.int32, device="cuda:0")
+
+      def decode(i):
+        extras = Sampler.pack(params, list(range(batch)), [i] * batch)
+        engine.runner.step_and_sample([StepItem(r, [1], (0,)) for r in rids], extras, Sampler.sample, tokens_dev,
+                                      sampling_pad=Sampler.PAD_ROWS)
+
+      for i in range(4):
+        decode(i)
+      torch.cuda.synchronize()
+      dtimes = _kernel_times(lambda i: decode(10 + i), 4)
+      dk = _famupel_groups(dtimes)
+      for r in rids:
+        engine.cache.release_request(r)
+      g = torch.Generator().manual_seed(7)
+
+      def whole(i):
+        rid = f"rates{i}"
+        engine.cache.admit(rid)
+        engine.runner.step([StepItem(rid, torch.randint(0, COMPARE_VOCAB, (T,), generator=g).tolist(), (T - 1,))])
+        engine.cache.release_request(rid)
+
+      for i in range(2):
+        whole(i)
+      torch.cuda.synchronize()
+      ptimes = _kernel_times(lambda i: whole(10 + i), 2)
+      pt = _famupel_groups(ptimes)
+      for grp in (pt, dk):
+        for key in grp:
+          grp[key] = max(grp[key], 1e-9)
+      gl, rt, S = size["gla"], size["ret"], size["streams"]
+      n_side, n_gla = L // 3, L - L // 3
+      ff_w = L * 2 * (size["ff"] * 3 // 2) * W
+      seen_all = sum(t + 1 for t in range(T))
+      attn_flops = n_side * 4.0 * H * hd * seen_all
+      attn_bytes = batch * CONTEXT * n_side * 2 * G * hd * 2
+      gh, gd, gv, rk = gl["heads"], gl["dim"], gl["vdim"], gl["rank"]
+      rh, rd, rv = rt["heads"], rt["dim"], rt["vdim"]
+      gla_w = (rk + 2 * gh * gd + 2 * gh * gv) * W + gh * gd * rk + W * gh * gv
+      left_w = (2 * H + 2 * G) * hd * W + W * H * hd
+      right_w = (2 * rh * rd + 2 * rh * rv) * W + W * rh * rv
+      proj_w = n_gla * gla_w + n_side * (left_w + right_w)
+      # what the recurrences must move: queries, keys, values, gates and outputs once (2 bytes a value), the decays' logits
+      # (4 bytes) and, in a decode step, every request's state in and out (4 bytes a value)
+      lin_io = n_gla * ((2 * gh * gd + 3 * gh * gv) * 2 + gh * gd * 4) + n_side * (2 * rh * rd + 3 * rh * rv) * 2
+      lin_state = (n_gla * gh * gd * gv + n_side * rh * rd * rv) * 4 * 2
+      # the streams: every sublayer reads and writes S float32 rows of the width, reads the sublayer's output and writes its input
+      sublayers = 2 * L
+      stream_bytes = sublayers * (2 * S * W * 4 + 2 * W * 2)
+      dense_w = ff_w + proj_w + COMPARE_VOCAB * W
+      out = {"prefill_attention": {"us": round(pt["attention"], 1), "TFLOP/s": round(attn_flops / pt["attention"] / 1e6, 1),
+                                   "frac": round(attn_flops / pt["attention"] / 1e6 / pk["bf16_tflops"], 4)},
+             "decode_attention": {"us": round(dk["attention"], 1), "GB/s": round(attn_bytes / dk["attention"] / 1e3, 1),
+                                  "frac": round(attn_bytes / dk["attention"] / 1e3 / pk["hbm_gbs"], 4)},
+             "prefill_dense_products": {"us": round(pt["dense_products"], 1),
+                                        "TFLOP/s": round(2.0 * T * (ff_w + proj_w) / pt["dense_products"] / 1e6, 1),
+                                        "frac": round(2.0 * T * (ff_w + proj_w) / pt["dense_products"] / 1e6 / pk["bf16_tflops"], 4)},
+             "decode_dense_products": {"us": round(dk["dense_products"], 1), "GB/s": round(2.0 * dense_w / dk["dense_products"] / 1e3, 1),
+                                       "frac": round(2.0 * dense_w / dk["dense_products"] / 1e3 / pk["hbm_gbs"], 4)},
+             "prefill_linear_attention": {"us": round(pt["linear_attention"], 1), "GB/s": round(T * lin_io / pt["linear_attention"] / 1e3, 1),
+                                          "frac": round(T * lin_io / pt["linear_attention"] / 1e3 / pk["hbm_gbs"], 4)},
+             "decode_linear_attention": {"us": round(dk["linear_attention"], 1),
+                                         "GB/s": round(batch * (lin_io + lin_state) / dk["linear_attention"] / 1e3, 1),
+                                         "frac": round(batch * (lin_io + lin_state) / dk["linear_attention"] / 1e3 / pk["hbm_gbs"], 4)},
+             "prefill_streams": {"us": round(pt["streams"], 1), "GB/s": round(T * stream_bytes / pt["streams"] / 1e3, 1),
+                                 "frac": round(T * stream_bytes / pt["streams"] / 1e3 / pk["hbm_gbs"], 4)},
+             "decode_streams_us": round(dk["streams"], 1),
+             "other_us": {"prefill": round(pt["other"], 1), "decode": round(dk["other"], 1)}}
+
+      def top(times):
+        rows = sorted(((us, n) for n, us in times.items() if not n.startswith("Mem")), reverse=True)[:14]
+        return [[round(us, 1), n.replace("(anonymous namespace)::", "")[:70]] for us, n in rows]
+
+      out["top_kernels_us"] = {"prefill": top(ptimes), "decode": top(dtimes)}
+    engine.stop()
+    del engine
+    gc.collect()
+    torch.cuda.empty_cache()
+  return out
+
+
 def compare_designs(args) -> int:
-  """``--compare rikanex`` / ``--compare vugudra``: the design beside the Qwen3 dense decoder at equal sizes (random weights): prefill of
+  """``--compare rikanex`` / ``--compare vugudra``: the design beside the Qwen3 dense decoder at equal sizes (random weights);
+  ``--compare famupel``: the design beside Vugudra, the closest of the engine's designs, at equal sizes: prefill of
   one 2048-token prompt and decode steps at ``--batch`` requests with ``--context``-token contexts, and, from a process of
   its own with dependent launch off, what the kinds of kernels of both reach against the measured peaks."""
   pk = peaks()
@@ -1026,9 +1208,10 @@ def compare_designs(args) -> int:
   MAX_MODEL_LEN = max(MAX_MODEL_LEN, -(-(CONTEXT + GENERATED + 128) // 1024) * 1024)
   sizes = [x for x in args.sizes.split(",") if x]
   design = args.compare
-  sizes_of, configs_of, one = ((COMPARE_SIZES, compare_configs, compare_one) if design == "rikanex" else
-                               (VUGUDRA_SIZES, vugudra_configs, vugudra_one))
-  result = {"compare": f"{design} beside qwen3 at equal sizes", "batch": args.batch, "context": CONTEXT, "window": COMPARE_WINDOW,
+  sizes_of, configs_of, one = {"rikanex": (COMPARE_SIZES, compare_configs, compare_one), "vugudra": (VUGUDRA_SIZES, vugudra_configs, vugudra_one),
+                               "famupel": (FAMUPEL_SIZES, famupel_configs, famupel_one)}[design]
+  beside = "vugudra" if design == "famupel" else "qwen3"
+  result = {"compare": f"{design} beside {beside} at equal sizes", "batch": args.batch, "context": CONTEXT, "window": COMPARE_WINDOW,
             "vocab": COMPARE_VOCAB, "prefill_tokens": PREFILL_TOKENS, "steps": args.steps, "warmup": warmup, "dtype": "bf16",
             "data": "synthetic: random weights, uniform random token ids", "peaks": pk["source"], "sizes": {}}
   kernels_child = args.impl == "compare-child"
@@ -1051,7 +1234,7 @@ def compare_designs(args) -> int:
     if found:
       child = json.loads(found[-1])
       for tag in sizes:
-        for name in ("qwen3", design):
+        for name in (beside, design):
           result["sizes"][tag][name]["kernels"] = child["sizes"][tag][name]
     else:
       result["kernels_unavailable"] = (proc.stderr or "no output").strip().splitlines()[-1][:300]
@@ -1066,8 +1249,8 @@ def main() -> int:
   ap.add_argument("--steps", type=int, default=128)
   ap.add_argument("--warmup", type=int, default=8)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-child", "kernels-child", "compare-child"])
-  ap.add_argument("--compare", default=None, choices=["rikanex", "vugudra"],
-                  help="time the Rikanex or the Vugudra design beside the Qwen3 dense decoder at equal sizes (--sizes), print one JSON line and exit")
+  ap.add_argument("--compare", default=None, choices=["rikanex", "vugudra", "famupel"],
+                  help="time the Rikanex or the Vugudra design beside the Qwen3 dense decoder, or the Famupel design beside Vugudra, at equal sizes (--sizes), print one JSON line and exit")
   ap.add_argument("--sizes", default="s,m,l", help="with --compare: which of the sizes s, m, l (commas between them)")
   ap.add_argument("--batch", type=int, default=8)
   ap.add_argument("--shape", default="0.6b", choices=sorted(SHAPES), help="layer sizes: the default, or another Qwen3 model's")

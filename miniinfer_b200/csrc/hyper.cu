@@ -15,12 +15,49 @@ namespace {
 
 constexpr int HYPER_MAX_STREAMS = 8;
 
-template <typename TOut, typename TDelta>
+// VEC values of a row at a time: 16-byte accesses to the float32 streams when the width is a multiple of 4
+template <int VEC> __device__ __forceinline__ void hyper_load(float (&v)[VEC], const float* p) {
+  if constexpr (VEC == 4) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+    v[0] = p[0];
+  }
+}
+template <int VEC> __device__ __forceinline__ void hyper_load(float (&v)[VEC], const __nv_bfloat16* p) {
+  if constexpr (VEC == 4) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x), b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+    v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+  } else {
+    v[0] = __bfloat162float(p[0]);
+  }
+}
+template <int VEC> __device__ __forceinline__ void hyper_store(float* p, const float (&v)[VEC]) {
+  if constexpr (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  else p[0] = v[0];
+}
+template <int VEC> __device__ __forceinline__ void hyper_store(__nv_bfloat16* p, const float (&v)[VEC]) {
+  if constexpr (VEC == 4) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 t;
+    t.x = *reinterpret_cast<const unsigned*>(&a);
+    t.y = *reinterpret_cast<const unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = t;
+  } else {
+    p[0] = __float2bfloat16_rn(v[0]);
+  }
+}
+
+// SC: the number of streams when it is 1 to 4 (loops over streams unroll to exactly that), 0: any number up to the limit
+template <typename TOut, typename TDelta, int SC, int VEC>
 __global__ void __launch_bounds__(256)
 hyper_connection_kernel(TOut* __restrict__ res, float* __restrict__ streams, const TDelta* __restrict__ y,
                         const float* __restrict__ mix, const float* __restrict__ outw, const float* __restrict__ inw,
-                        const float* __restrict__ w, const int* __restrict__ rows, int S, int W, float eps, int write_back) {
-  extern __shared__ float hyper_u[];
+                        const float* __restrict__ w, const int* __restrict__ rows, int S_any, int W, float eps, int write_back) {
+  constexpr int MAXS = SC ? SC : HYPER_MAX_STREAMS;
+  const int S = SC ? SC : S_any;
+  extern __shared__ __align__(16) float hyper_u[];
   __shared__ float scratch[33];
   __shared__ float s_mix[HYPER_MAX_STREAMS * HYPER_MAX_STREAMS], s_out[HYPER_MAX_STREAMS], s_in[HYPER_MAX_STREAMS];
   // the weights: no kernel writes them
@@ -36,40 +73,69 @@ hyper_connection_kernel(TOut* __restrict__ res, float* __restrict__ streams, con
   float* x = streams + (size_t)row * S * W;
   const TDelta* yr = y ? y + (size_t)row * W : nullptr;
   float ss = 0.f;
-  for (int h = threadIdx.x; h < W; h += blockDim.x) {
-    float old[HYPER_MAX_STREAMS], now[HYPER_MAX_STREAMS];
+  for (int h = threadIdx.x * VEC; h < W; h += blockDim.x * VEC) {
+    float old[MAXS][VEC], now[MAXS][VEC];
 #pragma unroll
-    for (int s = 0; s < HYPER_MAX_STREAMS; ++s) old[s] = s < S ? x[(size_t)s * W + h] : 0.f;
+    for (int s = 0; s < MAXS; ++s) {
+      if (s < S) {
+        hyper_load<VEC>(old[s], x + (size_t)s * W + h);
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) old[s][e] = 0.f;
+      }
+    }
     if (yr) {
-      const float yv = mi::to_float(yr[h]);
+      float yv[VEC];
+      hyper_load<VEC>(yv, yr + h);
 #pragma unroll
-      for (int t = 0; t < HYPER_MAX_STREAMS; ++t) {
+      for (int t = 0; t < MAXS; ++t) {
         if (t >= S) continue;
-        float acc = 0.f;
 #pragma unroll
-        for (int s = 0; s < HYPER_MAX_STREAMS; ++s)
-          if (s < S) acc = fmaf(s_mix[s * S + t], old[s], acc);
-        now[t] = fmaf(s_out[t], yv, acc);
-        if (write_back) x[(size_t)t * W + h] = now[t];
+        for (int e = 0; e < VEC; ++e) {
+          float acc = 0.f;
+#pragma unroll
+          for (int s = 0; s < MAXS; ++s)
+            if (s < S) acc = fmaf(s_mix[s * S + t], old[s][e], acc);
+          now[t][e] = fmaf(s_out[t], yv[e], acc);
+        }
+        if (write_back) hyper_store<VEC>(x + (size_t)t * W + h, now[t]);
       }
     } else {
 #pragma unroll
-      for (int t = 0; t < HYPER_MAX_STREAMS; ++t) now[t] = old[t];
-    }
-    float u = 0.f;
+      for (int t = 0; t < MAXS; ++t)
 #pragma unroll
-    for (int t = 0; t < HYPER_MAX_STREAMS; ++t)
-      if (t < S) u = fmaf(s_in[t], now[t], u);
-    hyper_u[h] = u;
-    ss = fmaf(u, u, ss);
+        for (int e = 0; e < VEC; ++e) now[t][e] = old[t][e];
+    }
+    float u[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      u[e] = 0.f;
+#pragma unroll
+      for (int t = 0; t < MAXS; ++t)
+        if (t < S) u[e] = fmaf(s_in[t], now[t][e], u[e]);
+      ss = fmaf(u[e], u[e], ss);
+    }
+    hyper_store<VEC>(hyper_u + h, u);
   }
   TOut* o = res + (size_t)r * W;
+  // every thread reads back the values it wrote itself
   if (w == nullptr) {
-    for (int h = threadIdx.x; h < W; h += blockDim.x) o[h] = mi::from_float<TOut>(hyper_u[h]);
+    for (int h = threadIdx.x * VEC; h < W; h += blockDim.x * VEC) {
+      float u[VEC];
+      hyper_load<VEC>(u, (const float*)hyper_u + h);
+      hyper_store<VEC>(o + h, u);
+    }
     return;
   }
   const float rstd = 1.f / sqrtf(mi::block_sum(ss, scratch) / (float)W + eps);
-  for (int h = threadIdx.x; h < W; h += blockDim.x) o[h] = mi::from_float<TOut>(w[h] * (hyper_u[h] * rstd));
+  for (int h = threadIdx.x * VEC; h < W; h += blockDim.x * VEC) {
+    float u[VEC], wv[VEC];
+    hyper_load<VEC>(u, (const float*)hyper_u + h);
+    hyper_load<VEC>(wv, w + h);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) u[e] = wv[e] * (u[e] * rstd);
+    hyper_store<VEC>(o + h, u);
+  }
 }
 
 }  // namespace
@@ -83,10 +149,20 @@ MI_API int mi_hyper_connection(void* res, int res_dtype, float* streams, const v
   if (R == 0) return 0;
   const size_t smem = (size_t)W * sizeof(float);
   MI_REQUIRE(smem <= 160 * 1024, "hyper_connection: rows of %d values do not fit shared memory", W);
+  const bool vec = W % 4 == 0;
+#define MI_HYPER_ONE(TO, TD, SC, VEC)                                                                                 \
+  do {                                                                                                                \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_connection_kernel<TO, TD, SC, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    mi::launch(hyper_connection_kernel<TO, TD, SC, VEC>, dim3(R), dim3(256), smem, stream, (TO*)res, streams, (const TD*)y, mix, outw, inw, w, rows, S, W, eps, write_back); \
+  } while (0)
 #define MI_HYPER(TO, TD)                                                                                              \
   do {                                                                                                                \
-    if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_connection_kernel<TO, TD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    mi::launch(hyper_connection_kernel<TO, TD>, dim3(R), dim3(256), smem, stream, (TO*)res, streams, (const TD*)y, mix, outw, inw, w, rows, S, W, eps, write_back); \
+    if (!vec) MI_HYPER_ONE(TO, TD, 0, 1);                                                                             \
+    else if (S == 1) MI_HYPER_ONE(TO, TD, 1, 4);                                                                      \
+    else if (S == 2) MI_HYPER_ONE(TO, TD, 2, 4);                                                                      \
+    else if (S == 3) MI_HYPER_ONE(TO, TD, 3, 4);                                                                      \
+    else if (S == 4) MI_HYPER_ONE(TO, TD, 4, 4);                                                                      \
+    else MI_HYPER_ONE(TO, TD, 0, 4);                                                                                  \
   } while (0)
   if (res_dtype == MI_BF16 && y_dtype == MI_BF16) MI_HYPER(__nv_bfloat16, __nv_bfloat16);
   else if (res_dtype == MI_F32 && y_dtype == MI_F32) MI_HYPER(float, float);
@@ -94,6 +170,7 @@ MI_API int mi_hyper_connection(void* res, int res_dtype, float* streams, const v
   else if (res_dtype == MI_F32 && y_dtype == MI_BF16) MI_HYPER(float, __nv_bfloat16);
   else return mi_fail("hyper_connection: unknown dtypes res=%d y=%d", res_dtype, y_dtype);
 #undef MI_HYPER
+#undef MI_HYPER_ONE
   MI_LAUNCH_OK("hyper_connection");
   return 0;
 }
