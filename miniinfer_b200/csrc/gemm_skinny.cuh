@@ -62,9 +62,15 @@ template <>
 __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 // out += the product rounded to bf16 (each element has one writer, so no atomics)
 __device__ __forceinline__ void add_out(float* p, float v) { *p += __bfloat162float(__float2bfloat16_rn(v)); }
+// max(product rounded to bf16, 0)^2: the value the product followed by the squared-ReLU kernel leaves
+__device__ __forceinline__ float relu2_out(float v) {
+  const float r = fmaxf(__bfloat162float(__float2bfloat16_rn(v)), 0.f);
+  return r * r;
+}
 template <int FUSE, typename TOut>
 __device__ __forceinline__ void put_out(TOut* p, float v) {
   if constexpr (FUSE == 2) add_out(p, v);
+  else if constexpr (FUSE == 3) store_out<TOut>(p, relu2_out(v));
   else store_out<TOut>(p, v);
 }
 
@@ -101,7 +107,9 @@ __device__ __forceinline__ float swiglu(float gate, float up) {
 //               row in an order that depends on K alone.
 //   FUSE_ADD    the residual add behind it: out is the float32 residual stream and receives
 //               out += bf16(product), the value the norm kernel adds when it is given the bf16 product.
-enum { FUSE_NONE = 0, FUSE_NORM = 1, FUSE_ADD = 2 };
+//   FUSE_RELU2  the squared ReLU of a feed-forward behind it: out = max(bf16(product), 0)^2, the value the
+//               product followed by the activation kernel leaves.
+enum { FUSE_NONE = 0, FUSE_NORM = 1, FUSE_ADD = 2, FUSE_RELU2 = 3 };
 
 struct FuseArgs {
   const float* xf;       // FUSE_NORM: residual rows [M, K]

@@ -4,6 +4,7 @@
 //   mi_gemm_skinny_norm_bf16         out = rmsnorm(resid) * w^T            the norm in the product's prologue
 //   mi_gemm_skinny_norm_swiglu_bf16  out = swiglu(rmsnorm(resid) * w^T)    the same, gate-and-up with the activation
 //   mi_gemm_skinny_add_f32           resid += bf16(x * w^T)                the residual add in the product's epilogue
+//   mi_gemm_skinny_relu2_bf16        out = max(bf16(x * w^T), 0)^2         a squared-ReLU feed-forward's activation in its up product
 //
 // The residual stream is float32.  The values are those of the unfused kernels up to the order of
 // the norm's sum of squares: the normalised activation is rounded to bf16 once, as the norm kernel
@@ -36,6 +37,15 @@ MI_API int mi_gemm_skinny_norm_swiglu_bf16(void* out, const float* resid, const 
   if (M == 0) return 0;
   return dispatch_swiglu16<FUSE_NORM>((__nv_bfloat16*)out, nullptr, (const __nv_bfloat16*)w, M, N, K, ldo, stream,
                                       FuseArgs{resid, norm_w, eps});
+}
+
+// out[M, N] = max(bf16(x w^T), 0)^2, bf16: the up product of a squared-ReLU feed-forward with the activation in its epilogue
+MI_API int mi_gemm_skinny_relu2_bf16(void* out, const void* x, const void* w, int M, int N, int K, int ldo, cudaStream_t stream) {
+  MI_SKINNY_FUSED_CHECKS("gemm_skinny_relu2")
+  MI_REQUIRE(((uintptr_t)x % 16) == 0, "gemm_skinny_relu2: the activations must be 16-byte aligned");
+  if (M == 0) return 0;
+  return dispatch16<__nv_bfloat16, FUSE_RELU2>((__nv_bfloat16*)out, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, M, N, K, ldo, stream,
+                                               FuseArgs{nullptr, nullptr, 0.f});
 }
 
 MI_API int mi_gemm_skinny_add_f32(float* resid, const void* x, const void* w, int M, int N, int K, int ldo, cudaStream_t stream) {

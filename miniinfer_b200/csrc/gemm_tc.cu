@@ -76,6 +76,7 @@ struct Args {
   // those rows are multiplied with, or -1 for rows nobody owns (such tiles are passed over by all three roles alike).
   const int* tile_expert;
   int tile_rows, expert_rows;
+  int act;               // plain product only: 1 - out = max(bf16(product), 0)^2, the squared ReLU of a feed-forward; 0 - the product
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -371,6 +372,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
             const float gg = round_bf16(g[i]), uu = round_bf16(u[i]);
             g[i] = mi::silu_mul_fast(gg, uu);
           }
+        } else if (a.act == 1) {
+          // the values the product followed by the activation kernel leaves: rounded, clamped, squared
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float r = fmaxf(round_bf16(g[i]), 0.f);
+            g[i] = r * r;
+          }
         }
         if (c == TILE_COLS / 32 - 1) {
           // the accumulator has been read: the products of the tile after next may overwrite it
@@ -489,7 +497,7 @@ int launch_tc(const CUtensorMap& xm, const CUtensorMap& wm, const Args& a, int s
 
 template <bool SWIGLU, bool GROUPED = false>
 int run(void* out, const void* x, const void* w, int M, int N, int K, int ldo, int* status, int pairs, cudaStream_t stream,
-        int experts = 1, const int* tile_expert = nullptr, int tile_rows = 0) {
+        int experts = 1, const int* tile_expert = nullptr, int tile_rows = 0, int act = 0) {
   // N: output columns; w has N rows (plain) or 2 N rows (SwiGLU), per expert
   MI_REQUIRE(M > 0 && N > 0 && K >= BK && K % 8 == 0 && N % 8 == 0 && ldo % 8 == 0 && ldo >= N,
              "gemm_tc: M=%d N=%d K=%d ldo=%d: K (at least 64), N and the row stride must be multiples of 8", M, N, K, ldo);
@@ -500,6 +508,7 @@ int run(void* out, const void* x, const void* w, int M, int N, int K, int ldo, i
   Args a;
   a.tile_expert = tile_expert;
   a.tile_rows = tile_rows;
+  a.act = SWIGLU ? 0 : act;
   a.expert_rows = SWIGLU ? 2 * N : N;
   a.out = (__nv_bfloat16*)out;
   a.status = status;
@@ -546,4 +555,10 @@ MI_API int mi_gemm_tc_grouped_bf16(void* out, const void* x, const void* w, int 
 MI_API int mi_gemm_tc_bf16(void* out, const void* x, const void* w, int M, int N, int K, int ldo, int* status,
                            int pairs, cudaStream_t stream) {
   return run<false>(out, x, w, M, N, K, ldo, status, pairs, stream);
+}
+
+// out[M, N] = max(bf16(x w^T), 0)^2, all bf16: the up product of a squared-ReLU feed-forward with the activation in its epilogue.
+MI_API int mi_gemm_tc_relu2_bf16(void* out, const void* x, const void* w, int M, int N, int K, int ldo, int* status,
+                                 int pairs, cudaStream_t stream) {
+  return run<false>(out, x, w, M, N, K, ldo, status, pairs, stream, 1, nullptr, 0, 1);
 }

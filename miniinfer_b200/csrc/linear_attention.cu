@@ -90,6 +90,13 @@ __device__ __forceinline__ void lin_copy4(float* dst, const float* src, bool tak
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
 }
 
+// 16 bytes at a time (both addresses 16-byte aligned)
+__device__ __forceinline__ void lin_copy16(float* dst, const float* src, bool take) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  const int bytes = take ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+
 constexpr int LIN_THREADS = 128;
 constexpr int LIN_CHUNK = 16;            // tokens whose vectors are in shared memory at a time
 constexpr int LIN_SEGMENTS = 16;
@@ -158,8 +165,32 @@ linear_recurrence_kernel(LinArgs a) {
   // Rows past dim and columns past vdim are filled with zeros (a zero key and query row leave such a row of S at zero
   // and out of the sums).
   const int chunk_floats = LIN_CHUNK * tok_floats;
+  // Sizes that are multiples of 4 move 16 bytes a copy (the scratch rows then start on 16-byte boundaries); the first
+  // pass of the stretches does not read the queries.
+  const bool vec4 = dim % 4 == 0 && vdim % 4 == 0 && cols % 4 == 0;
+  const int per = R * DK / 4, per_shift = __ffs(per) - 1;          // 16-byte pieces of a padded vector: a power of two
+  const int cq = cols / 4, cq_shift = __ffs(cq > 0 ? cq : 1) - 1;
   auto fetch = [&](int c0, float* buf) {
     const int n = min(LIN_CHUNK, n_new - c0);
+    if (vec4) {
+      for (int idx = threadIdx.x; idx < n * per; idx += LIN_THREADS) {
+        const int tt = idx >> per_shift, i = (idx & (per - 1)) * 4;
+        const size_t t = (size_t)(row0 + c0 + tt);
+        float* base = buf + (size_t)tt * tok_floats + (i / DK) * LD + (i % DK);
+        const bool in = i < dim;
+        const size_t at = (t * a.heads + head) * dim + (in ? i : 0);
+        if (MODE != 1) lin_copy16(base, a.qn + at, in);
+        lin_copy16(base + vec, a.kn + at, in);
+        if (CHANNEL) lin_copy16(base + 2 * vec, a.g + at, in);
+      }
+      for (int idx = threadIdx.x; idx < n * cq; idx += LIN_THREADS) {
+        const int tt = idx >> cq_shift, j = (idx & (cq - 1)) * 4;
+        const int c = blockIdx.z * cols + j;
+        lin_copy16(buf + (size_t)tt * tok_floats + NV * vec + j, a.raw + (size_t)(row0 + c0 + tt) * (a.heads * vdim) + head * vdim + (c < vdim ? c : 0), c < vdim);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      return;
+    }
     for (int idx = threadIdx.x; idx < n * R * DK; idx += LIN_THREADS) {
       const int tt = idx / (R * DK), i = idx % (R * DK);
       const size_t t = (size_t)(row0 + c0 + tt);
@@ -241,12 +272,21 @@ linear_carry_kernel(float* __restrict__ seg_state, const float* __restrict__ seg
   float* st = state + (size_t)slot * state_stride + (size_t)head * dim * vdim;
   for (int e = blockIdx.z * blockDim.x + threadIdx.x; e < dim * vdim; e += gridDim.z * blockDim.x) {
     const int i = e / vdim;
-    float c = st[e];
-    for (int s = 0; s < nseg; ++s) {
+    // every stretch's end state and decay first, all loads in flight at once; then the chain, which is arithmetic only
+    float end[LIN_SEGMENTS], dec[LIN_SEGMENTS];
+#pragma unroll
+    for (int s = 0; s < LIN_SEGMENTS; ++s) {
       const size_t at = ((size_t)(item * LIN_SEGMENTS + s) * heads + head) * dim;
-      const float end = seg_state[at * vdim + e];
+      end[s] = s < nseg ? seg_state[at * vdim + e] : 0.f;
+      dec[s] = s < nseg ? seg_decay[at + i] : 1.f;
+    }
+    float c = st[e];
+#pragma unroll
+    for (int s = 0; s < LIN_SEGMENTS; ++s) {
+      if (s >= nseg) break;
+      const size_t at = ((size_t)(item * LIN_SEGMENTS + s) * heads + head) * dim;
       seg_state[at * vdim + e] = c;
-      c = fmaf(seg_decay[at + i], c, end);
+      c = fmaf(dec[s], c, end[s]);
     }
     st[e] = c;
   }
@@ -362,7 +402,7 @@ MI_API int mi_linear_attention(void* out, int ldo, const void* q, int ldq, const
       }                                                                                                              \
       dim3 sgrid(heads, items * LIN_SEGMENTS, rgrid.z);                                                              \
       mi::launch(linear_recurrence_kernel<DKV, 1, CH>, sgrid, dim3(LIN_THREADS), smem, stream, d);                   \
-      const int cz = (dim * vdim + 255) / 256 > 8 ? 8 : (dim * vdim + 255) / 256;                                    \
+      const int cz = (dim * vdim + 255) / 256 > 64 ? 64 : (dim * vdim + 255) / 256;                                    \
       mi::launch(linear_carry_kernel, dim3(heads, items, cz), dim3(256), 0, stream, d.seg_state, (const float*)d.seg_decay, state, \
                  state_stride, q_len, seq_slot, heads, dim, vdim);                                                   \
       mi::launch(linear_recurrence_kernel<DKV, 2, CH>, sgrid, dim3(LIN_THREADS), smem, stream, d);                   \

@@ -722,6 +722,35 @@ def relu_squared(out: torch.Tensor, x: torch.Tensor) -> None:
   _check(lib, lib.mi_relu_squared(_ptr(out), _ptr(x), _dt(x), ctypes.c_longlong(x.numel()), _stream()))
 
 
+def linear_relu_squared(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace, force_tc: bool = False) -> None:
+  """out[M, N] = max(x @ w^T, 0)^2: the up product of a squared-ReLU feed-forward.  bfloat16 with M <= 16 (below the
+  sizes of the weight-streaming tcgen05 kernel) or from 1280 rows on (1792 for K < 4096): one kernel, the activation in
+  the product's epilogue (few rows: the mma.sync kernel; many: the tcgen05 kernel) - the product is rounded to bfloat16
+  before it is clamped and squared, so the values are those of the product followed by the activation kernel, which is
+  what runs otherwise (``MINIINFER_B200_RELU2_FUSED=0``: always)."""
+  M, K = x.shape
+  N = w.shape[0]
+  if w.shape[1] != K or out.shape != (M, N) or out.dtype != x.dtype:
+    raise KernelError(f"linear_relu_squared: shapes do not match: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+  if M == 0:
+    return
+  fits = (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K >= 64 and K % 8 == 0 and N % 8 == 0 and x.is_contiguous()
+          and w.is_contiguous() and out.is_contiguous() and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
+          and os.environ.get("MINIINFER_B200_RELU2_FUSED", "1") != "0")
+  if fits and M <= SKINNY_BEST_M and not _streams(M, N, K, False, False):
+    lib = common_lib()
+    _check(lib, lib.mi_gemm_skinny_relu2_bf16(_ptr(out), _ptr(x), _ptr(w), M, N, K, N, _stream()))
+    return
+  many = force_tc or M >= (GEMM_TC_MIN_M if K >= 4096 else GEMM_TC_MIN_M_NARROW)
+  if fits and many and os.environ.get("MINIINFER_B200_GEMM_TC", "1") != "0":
+    lib = common_lib()
+    status = workspace.zeros("gemm_tc_status", 1, torch.int32)
+    _check(lib, lib.mi_gemm_tc_relu2_bf16(_ptr(out), _ptr(x), _ptr(w), M, N, K, N, _ptr(status, torch.int32), _tc_pairs(), _stream()))
+    return
+  linear(out, x, w)
+  relu_squared(out, out)
+
+
 def scaled_pair_sum(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor, scale_a: float, scale_b: float) -> None:
   """out = scale_a * a + scale_b * b element by element, in float32, rounded once."""
   lib = common_lib()

@@ -91,8 +91,7 @@ class ActivatedFeedForward(FeedForward):
   def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
     T = x.shape[0]
     act = ctx.ws.buffer("ffn_act", (T, self.intermediate_size), ctx.dtype)
-    ops.linear(act, x, self.up)
-    ops.relu_squared(act, act)
+    ops.linear_relu_squared(act, x, self.up, ctx.ws)
     out = ctx.ws.buffer("ffn_out", (T, self.hidden_size), ctx.dtype)
     ops.linear(out, act, self.down)
     return out

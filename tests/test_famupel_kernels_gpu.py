@@ -255,6 +255,39 @@ def test_small_elementwise_kernels(dtype):
   assert torch.equal(rows.cpu(), table[ids.long()].float().repeat(1, 3))
 
 
+@pytest.mark.parametrize("M,N,K,force_tc", [(1, 72, 64, False), (8, 520, 192, False), (16, 2056, 256, False), (40, 136, 96, False),
+                                            (300, 264, 128, True), (1800, 520, 320, False)])
+def test_up_product_with_the_squared_relu_in_its_epilogue(M, N, K, force_tc, monkeypatch):
+  """Few rows (the mma.sync kernel), many rows (the tcgen05 kernel) and what lies between (product, then activation) give
+  max(bfloat16(x w^T), 0)^2; a fused kernel gives bit for bit what the same product followed by the activation kernel gives."""
+  from miniinfer_b200.engine.context import Workspace
+  from miniinfer_b200.kernels import ops
+  g = torch.Generator().manual_seed(M + N)
+  x = torch.randn((M, K), generator=g).to(torch.bfloat16)
+  w = (torch.randn((N, K), generator=g) / K ** 0.5).to(torch.bfloat16)
+  ws = Workspace(torch.device(DEV))
+  out = torch.zeros((M, N), dtype=torch.bfloat16, device=DEV)
+  ops.linear_relu_squared(out, x.to(DEV), w.to(DEV), ws, force_tc=force_tc)
+  prod = x.float() @ w.float().t()
+  want = torch.relu(prod.to(torch.bfloat16).float()) ** 2
+  # a product within a rounding step of a bfloat16 boundary may round either way: two steps of the squared value
+  assert float(((out.float().cpu() - want).abs() / (want.abs() + 0.05)).max()) <= 2.5e-2
+  assert float(out.float().min()) >= 0.0
+  # the same product kernel, unfused
+  two = torch.zeros_like(out)
+  if M <= 16:
+    ops.linear(two, x.to(DEV), w.to(DEV))
+  elif force_tc or M >= 1792:
+    ops.linear_tc(two, x.to(DEV), w.to(DEV), ws)
+  else:
+    monkeypatch.setenv("MINIINFER_B200_RELU2_FUSED", "0")
+    ops.linear_relu_squared(two, x.to(DEV), w.to(DEV), ws)
+    assert torch.equal(two, out)
+    return
+  ops.relu_squared(two, two)
+  assert torch.equal(two, out)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,D,Dv,rot_dims", [(4, 1, 24, 16, 16), (2, 2, 16, 32, 8), (6, 3, 32, 32, 32), (2, 1, 128, 64, 32)])
 def test_biases_norm_over_the_whole_projection_and_rotation(dtype, H, G, D, Dv, rot_dims):

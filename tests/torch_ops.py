@@ -380,6 +380,11 @@ def relu_squared(out, x):
   out.copy_((torch.relu(x.float()) ** 2).to(out.dtype))
 
 
+def linear_relu_squared(out, x, w, workspace, force_tc=False):
+  linear(out, x, w)
+  relu_squared(out, out)
+
+
 def scaled_pair_sum(out, a, b, scale_a, scale_b):
   out.copy_((scale_a * a.float() + scale_b * b.float()).to(out.dtype))
 
@@ -477,5 +482,5 @@ def install(monkeypatch) -> None:
   for name in ("embedding", "add_rmsnorm", "add_layernorm", "linear", "linear_swiglu", "qk_norm_rope_store", "qkv_norm_mix_store",
                "attention", "routed_experts", "silu_mul", "sample", "linear_normed", "linear_swiglu_normed", "linear_add",
                "add_rmsnorm_pair", "rms_pair_sum", "linear_batched", "causal_conv", "selective_scan", "gated_delta", "latent_down",
-               "latent_query", "linear_attention", "hyper_connection", "relu_squared", "scaled_pair_sum"):
+               "latent_query", "linear_attention", "hyper_connection", "relu_squared", "linear_relu_squared", "scaled_pair_sum"):
     monkeypatch.setattr(ops, name, globals()[name])
