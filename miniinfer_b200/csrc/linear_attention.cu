@@ -12,8 +12,10 @@
 // with value i + rot_dims / 2) and scaled, the decays g = sigmoid(z)^(1/tau) = exp(logsigmoid(z) / tau) from their
 // logits z = a + bias, the values - as float32 rows.  (2) linear_recurrence, the only part that walks the tokens in
 // order: a block per (item, head, group of value columns); thread (j, r) keeps rows r * DK .. r * DK + DK - 1 of
-// column j of S in registers, the R threads of a column are neighbouring lanes and add their partial sums by
-// shuffles; the tokens' vectors come through shared memory in chunks, by asynchronous copies into two buffers.
+// CPT neighbouring columns of S in registers (four, so that a query, key and decay value fetched from shared memory
+// serves four multiply-adds: with one column a thread the kernel was bound by shared-memory loads), the R threads of
+// a column are neighbouring lanes and add their partial sums by shuffles; the tokens' vectors come through shared
+// memory in chunks, by asynchronous copies into two buffers.
 // (3) linear_output, a warp per (token, head): root mean square over the head, weight, gate.
 //
 // Everything between the projections and the gate is float32: angles (a table made on the host), decays and their
@@ -127,7 +129,7 @@ struct LinArgs {
 // of its decays, row by row) x (the state it starts from) + (its end state from a zero start).  MODE 1 walks every
 // stretch from zero and keeps the end state and the product; the carry kernel chains the stretches; MODE 2 walks every
 // stretch again from the state it really starts from and writes the read-outs.
-template <int DK, int MODE, bool CHANNEL>
+template <int DK, int CPT, int MODE, bool CHANNEL>
 __global__ void __launch_bounds__(LIN_THREADS)
 linear_recurrence_kernel(LinArgs a) {
   extern __shared__ __align__(16) float sm[];
@@ -146,20 +148,20 @@ linear_recurrence_kernel(LinArgs a) {
     n_new = max(0, min(len, n_new - seg * len));
   }
   const int R = a.R, dim = a.dim, vdim = a.vdim;
-  const int cols = LIN_THREADS / R;
+  const int cols = LIN_THREADS / R * CPT;                 // value columns of the block, CPT neighbouring ones a thread
   const int cl = threadIdx.x / R, r = threadIdx.x % R;
-  const int col = blockIdx.z * cols + cl;
-  const bool live = col < vdim;
+  const int col = blockIdx.z * cols + cl * CPT;            // the thread's first column
   const int vec = R * LD;                                  // floats of one padded vector
   const int tok_floats = NV * vec + cols;                  // q, k, (g,) the block's values
   mi::grid_dependency_sync();
   const size_t seg_at = ((size_t)(item * LIN_SEGMENTS + seg) * a.heads + head) * dim;
   float* st = MODE == 0 ? a.state + (size_t)slot * a.state_stride + (size_t)head * dim * vdim : a.seg_state + seg_at * vdim;
-  float S[DK], P[MODE == 1 ? DK : 1];
+  float S[CPT][DK], P[MODE == 1 ? DK : 1];
 #pragma unroll
   for (int i = 0; i < DK; ++i) {
     const int row = r * DK + i;
-    S[i] = (MODE != 1 && live && row < dim) ? st[(size_t)row * vdim + col] : 0.f;
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) S[c][i] = (MODE != 1 && col + c < vdim && row < dim) ? st[(size_t)row * vdim + col + c] : 0.f;
     if (MODE == 1) P[i] = 1.f;
   }
   // Rows past dim and columns past vdim are filled with zeros (a zero key and query row leave such a row of S at zero
@@ -219,31 +221,89 @@ linear_recurrence_kernel(LinArgs a) {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
-    for (int tt = 0; tt < n; ++tt) {
+    // One token: the state's rows of this thread decay and take the token's key x value; returns the thread's part of
+    // the read-out (MODE 1: nothing is read out).
+    auto token = [&](int tt, float (&o)[CPT]) {
       const float* base = cur + (size_t)tt * tok_floats;
       const float4* qv = reinterpret_cast<const float4*>(base + r * LD);
       const float4* kv = reinterpret_cast<const float4*>(base + vec + r * LD);
       const float4* gv = reinterpret_cast<const float4*>(base + 2 * vec + r * LD);
-      const float vj = base[NV * vec + cl];
-      float os[4] = {0.f, 0.f, 0.f, 0.f};
+      float vj[CPT];
+      if constexpr (CPT == 4) {
+        const float4 v4 = *reinterpret_cast<const float4*>(base + NV * vec + cl * 4);
+        vj[0] = v4.x; vj[1] = v4.y; vj[2] = v4.z; vj[3] = v4.w;
+      } else {
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) vj[c] = base[NV * vec + cl * CPT + c];
+      }
+      float os[CPT][4];
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) os[c][0] = os[c][1] = os[c][2] = os[c][3] = 0.f;
 #pragma unroll
       for (int i = 0; i < DK / 4; ++i) {
-        const float4 k4 = kv[i], q4 = qv[i];
-        float4 g4 = make_float4(hd, hd, hd, hd);
+        const float4 k4 = kv[i];
+        float4 g4 = make_float4(hd, hd, hd, hd), q4 = make_float4(0.f, 0.f, 0.f, 0.f);
         if (CHANNEL) g4 = gv[i];
-        S[4 * i] = fmaf(g4.x, S[4 * i], k4.x * vj); S[4 * i + 1] = fmaf(g4.y, S[4 * i + 1], k4.y * vj);
-        S[4 * i + 2] = fmaf(g4.z, S[4 * i + 2], k4.z * vj); S[4 * i + 3] = fmaf(g4.w, S[4 * i + 3], k4.w * vj);
+        if (MODE != 1) q4 = qv[i];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+          float* Sc = S[c] + 4 * i;
+          Sc[0] = fmaf(g4.x, Sc[0], k4.x * vj[c]); Sc[1] = fmaf(g4.y, Sc[1], k4.y * vj[c]);
+          Sc[2] = fmaf(g4.z, Sc[2], k4.z * vj[c]); Sc[3] = fmaf(g4.w, Sc[3], k4.w * vj[c]);
+          if (MODE != 1) {
+            os[c][0] = fmaf(q4.x, Sc[0], os[c][0]); os[c][1] = fmaf(q4.y, Sc[1], os[c][1]);
+            os[c][2] = fmaf(q4.z, Sc[2], os[c][2]); os[c][3] = fmaf(q4.w, Sc[3], os[c][3]);
+          }
+        }
         if (MODE == 1) {
           P[4 * i] *= g4.x; P[4 * i + 1] *= g4.y; P[4 * i + 2] *= g4.z; P[4 * i + 3] *= g4.w;
-        } else {
-          os[0] = fmaf(q4.x, S[4 * i], os[0]); os[1] = fmaf(q4.y, S[4 * i + 1], os[1]);
-          os[2] = fmaf(q4.z, S[4 * i + 2], os[2]); os[3] = fmaf(q4.w, S[4 * i + 3], os[3]);
         }
       }
-      if (MODE != 1) {                        // the first pass of the stretches keeps the state only
-        float oj = (os[0] + os[1]) + (os[2] + os[3]);
-        for (int o = R >> 1; o > 0; o >>= 1) oj += __shfl_xor_sync(0xffffffffu, oj, o);
-        if (live && r == 0) a.raw[(size_t)(row0 + c0 + tt) * (a.heads * vdim) + head * vdim + col] = oj;
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) o[c] = (os[c][0] + os[c][1]) + (os[c][2] + os[c][3]);
+    };
+    float* orow = a.raw + (size_t)(row0 + c0) * (a.heads * vdim) + head * vdim + col;
+    constexpr int GROUP = 8;                 // tokens whose read-outs are added up together
+    if (DK == 16 && n == LIN_CHUNK) {          // (more rows a thread leave no registers for eight tokens at once)
+      // A whole chunk: its tokens unrolled, eight at a time, and the threads of a column add up the read-outs of all
+      // eight together - independent chains of shuffles instead of one after every token.  Token by token the sums
+      // are those of the loop below, in the same order.
+#pragma unroll
+      for (int t0 = 0; t0 < LIN_CHUNK; t0 += GROUP) {
+        float oj[GROUP][CPT];
+#pragma unroll
+        for (int tt = 0; tt < GROUP; ++tt) token(t0 + tt, oj[tt]);
+        if (MODE != 1) {
+          for (int o = R >> 1; o > 0; o >>= 1) {
+#pragma unroll
+            for (int tt = 0; tt < GROUP; ++tt)
+#pragma unroll
+              for (int c = 0; c < CPT; ++c) oj[tt][c] += __shfl_xor_sync(0xffffffffu, oj[tt][c], o);
+          }
+          if (r == 0) {
+#pragma unroll
+            for (int tt = 0; tt < GROUP; ++tt)
+#pragma unroll
+              for (int c = 0; c < CPT; ++c)
+                if (col + c < vdim) orow[(size_t)(t0 + tt) * (a.heads * vdim) + c] = oj[tt][c];
+          }
+        }
+      }
+    } else {
+      for (int tt = 0; tt < n; ++tt) {
+        float oj[CPT];
+        token(tt, oj);
+        if (MODE != 1) {                        // the first pass of the stretches keeps the state only
+          for (int o = R >> 1; o > 0; o >>= 1) {
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) oj[c] += __shfl_xor_sync(0xffffffffu, oj[c], o);
+          }
+          if (r == 0) {
+#pragma unroll
+            for (int c = 0; c < CPT; ++c)
+              if (col + c < vdim) orow[(size_t)tt * (a.heads * vdim) + c] = oj[c];
+          }
+        }
       }
     }
     __syncthreads();      // everyone is done with this buffer before the fetch after next fills it
@@ -253,7 +313,9 @@ linear_recurrence_kernel(LinArgs a) {
     for (int i = 0; i < DK; ++i) {
       const int row = r * DK + i;
       if (row >= dim) continue;
-      if (live) st[(size_t)row * vdim + col] = S[i];
+#pragma unroll
+      for (int c = 0; c < CPT; ++c)
+        if (col + c < vdim) st[(size_t)row * vdim + col + c] = S[c][i];
       if (MODE == 1 && col == 0) a.seg_decay[seg_at + row] = P[i];
     }
   }
@@ -326,6 +388,9 @@ MI_API long long mi_linear_attention_scratch_floats(int T, int heads, int dim, i
 
 MI_API int mi_linear_attention_segments() { return LIN_SEGMENTS; }
 
+// value columns a thread keeps beside one another: four while the state fits its registers
+static int lin_cpt(int DK) { return DK <= 32 ? 4 : 1; }
+
 static void lin_tiling(int dim, int* DK, int* R) {
   int dk = dim <= 128 ? 16 : 32, r = 1;
   for (;; dk *= 2) {
@@ -342,7 +407,7 @@ static void lin_tiling(int dim, int* DK, int* R) {
 MI_API int mi_linear_attention_blocks(int heads, int dim, int vdim) {
   int DK, R;
   lin_tiling(dim, &DK, &R);
-  const int cols = LIN_THREADS / (R > 32 ? 32 : R);
+  const int cols = LIN_THREADS / (R > 32 ? 32 : R) * lin_cpt(DK);
   return heads * ((vdim + cols - 1) / cols);
 }
 
@@ -371,7 +436,7 @@ MI_API int mi_linear_attention(void* out, int ldo, const void* q, int ldq, const
   lin_tiling(dim, &DK, &R);
   MI_REQUIRE(R <= 32, "linear_attention: dim=%d is more than a block's threads can keep", dim);
   const bool channel = a_in != nullptr;
-  const int cols = LIN_THREADS / R;
+  const int cols = LIN_THREADS / R * lin_cpt(DK);
   const int tok_floats = (channel ? 3 : 2) * R * (DK + 4) + cols;
   const size_t smem = (size_t)2 * LIN_CHUNK * tok_floats * sizeof(float);
   MI_REQUIRE(smem <= 200 * 1024, "linear_attention: a chunk's vectors (%zu bytes) do not fit shared memory", smem);
@@ -390,30 +455,30 @@ MI_API int mi_linear_attention(void* out, int ldo, const void* q, int ldq, const
   d.heads = heads; d.dim = dim; d.vdim = vdim; d.R = R;
   d.seg_state = segments;
   d.seg_decay = segments ? segments + (size_t)items * LIN_SEGMENTS * heads * dim * vdim : nullptr;
-#define MI_LIN_REC(DKV, CH)                                                                                          \
+#define MI_LIN_REC(DKV, CPTV, CH)                                                                                          \
   do {                                                                                                               \
     if (!segments) {                                                                                                 \
-      if (smem > 48 * 1024) cudaFuncSetAttribute(linear_recurrence_kernel<DKV, 0, CH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-      mi::launch(linear_recurrence_kernel<DKV, 0, CH>, rgrid, dim3(LIN_THREADS), smem, stream, d);                   \
+      if (smem > 48 * 1024) cudaFuncSetAttribute(linear_recurrence_kernel<DKV, CPTV, 0, CH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      mi::launch(linear_recurrence_kernel<DKV, CPTV, 0, CH>, rgrid, dim3(LIN_THREADS), smem, stream, d);                   \
     } else {                                                                                                         \
       if (smem > 48 * 1024) {                                                                                        \
-        cudaFuncSetAttribute(linear_recurrence_kernel<DKV, 1, CH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        cudaFuncSetAttribute(linear_recurrence_kernel<DKV, 2, CH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        cudaFuncSetAttribute(linear_recurrence_kernel<DKV, CPTV, 1, CH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        cudaFuncSetAttribute(linear_recurrence_kernel<DKV, CPTV, 2, CH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       }                                                                                                              \
       dim3 sgrid(heads, items * LIN_SEGMENTS, rgrid.z);                                                              \
-      mi::launch(linear_recurrence_kernel<DKV, 1, CH>, sgrid, dim3(LIN_THREADS), smem, stream, d);                   \
+      mi::launch(linear_recurrence_kernel<DKV, CPTV, 1, CH>, sgrid, dim3(LIN_THREADS), smem, stream, d);                   \
       const int cz = (dim * vdim + 255) / 256 > 64 ? 64 : (dim * vdim + 255) / 256;                                    \
       mi::launch(linear_carry_kernel, dim3(heads, items, cz), dim3(256), 0, stream, d.seg_state, (const float*)d.seg_decay, state, \
                  state_stride, q_len, seq_slot, heads, dim, vdim);                                                   \
-      mi::launch(linear_recurrence_kernel<DKV, 2, CH>, sgrid, dim3(LIN_THREADS), smem, stream, d);                   \
+      mi::launch(linear_recurrence_kernel<DKV, CPTV, 2, CH>, sgrid, dim3(LIN_THREADS), smem, stream, d);                   \
     }                                                                                                                \
   } while (0)
 #define MI_LIN_DK(CH)                                                                                                \
   do {                                                                                                               \
-    if (DK == 16) MI_LIN_REC(16, CH);                                                                                \
-    else if (DK == 32) MI_LIN_REC(32, CH);                                                                           \
-    else if (DK == 64) MI_LIN_REC(64, CH);                                                                           \
-    else MI_LIN_REC(128, CH);                                                                                        \
+    if (DK == 16) MI_LIN_REC(16, 4, CH);                                                                             \
+    else if (DK == 32) MI_LIN_REC(32, 4, CH);                                                                        \
+    else if (DK == 64) MI_LIN_REC(64, 1, CH);                                                                        \
+    else MI_LIN_REC(128, 1, CH);                                                                                     \
   } while (0)
 #define MI_LIN_ALL(TT)                                                                                               \
   do {                                                                                                               \
