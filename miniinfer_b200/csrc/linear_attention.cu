@@ -13,7 +13,7 @@
 // logits z = a + bias, the values - as float32 rows.  (2) linear_recurrence, the only part that walks the tokens in
 // order: a block per (item, head, group of value columns); thread (j, r) keeps rows r * DK .. r * DK + DK - 1 of
 // CPT neighbouring columns of S in registers (four, so that a query, key and decay value fetched from shared memory
-// serves four multiply-adds: with one column a thread the kernel was bound by shared-memory loads), the R threads of
+// serves four columns: with one column a thread the warps mostly waited on shared-memory loads), the R threads of
 // a column are neighbouring lanes and add their partial sums by shuffles; the tokens' vectors come through shared
 // memory in chunks, by asynchronous copies into two buffers.
 // (3) linear_output, a warp per (token, head): root mean square over the head, weight, gate.
