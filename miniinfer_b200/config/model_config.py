@@ -645,3 +645,176 @@ class FamupelConfig(ModelConfig):
       d["low_ranks"] = dict(self.low_ranks)
     d.update(self.extra)
     return d
+
+
+@dataclass
+class SigmoidAttentionConfig:
+  """``layers[i].mixer`` of a Luporax ``attention`` layer: grouped-query attention over every earlier token whose weights are
+  sigmoids of the capped scores (``softcap`` None: no cap)."""
+
+  heads: int
+  kv_heads: int
+  dim: int
+  vdim: int
+  scale: float
+  softcap: Optional[float]
+  rot: RotationConfig
+
+
+@dataclass
+class RglruConfig:
+  """``layers[i].mixer`` of a Luporax ``rglru`` layer: ``width`` channels in ``blocks`` equal parts, a convolution of ``conv`` taps."""
+
+  width: int
+  blocks: int
+  conv: int
+
+
+@dataclass
+class MinGruConfig:
+  """``layers[i].mixer`` of a Luporax ``mingru`` layer."""
+
+  width: int
+
+
+@dataclass
+class SharedExpertConfig:
+  ff: int
+  limit: float
+
+
+@dataclass
+class ClampedMoeConfig:
+  """``layers[i].mlp`` of a Luporax layer: ``experts`` experts of width ``ff`` with the clamp ``limit``, ``top`` of them a token,
+  and optionally a shared expert."""
+
+  ff: int
+  limit: float
+  experts: int
+  top: int
+  shared: Optional[SharedExpertConfig]
+
+
+@dataclass
+class LuporaxConfig(ModelConfig):
+  """Luporax: a decoder whose layers are listed one by one (``layers[i].{type, mixer, mlp}``).  A layer reads the residual
+  stream itself - its mixer through a token shift - and adds ``residual_mult`` times the RMS norm of each sublayer's output;
+  mixers of three types - ``attention`` (sigmoid weights on capped scores), ``rglru`` (a real-gated linear recurrent unit
+  behind a short convolution) and ``mingru`` (a minimal gated recurrence); the feed-forward is a mixture of clamped gated
+  experts with a gated shared expert, or absent.  A layer with ``weights_of: j`` has no tensors of its own and runs layer
+  ``j``'s, with a cache and state of its own.  The head is the embedding table, its logits times ``logit_scale``.  Other keys:
+  ``architecture``, ``vocab``, ``width``, ``norm.eps``.  The design has no position limit of its own;
+  ``max_position_embeddings`` is only the engine's bound."""
+
+  architecture: str = "Luporax"
+  vocab: int = 0
+  width: int = 0
+  norm: Dict[str, Any] = field(default_factory=dict)
+  residual_mult: Any = None
+  logit_scale: Any = None
+  layers: List[Dict[str, Any]] = field(default_factory=list)
+  max_position_embeddings: int = 1 << 30
+  initializer_range: float = 0.02
+
+  TYPES = ("attention", "rglru", "mingru")
+
+  def validate(self) -> None:
+    if not self.architectures:
+      self.architectures = [self.architecture]
+    self.vocab_size = self.vocab
+    for key in ("vocab", "width"):
+      v = getattr(self, key)
+      if not isinstance(v, int) or isinstance(v, bool) or v <= 0:
+        raise ConfigError(f"{key} must be a positive integer, got {v!r}")
+    eps = self.norm.get("eps") if isinstance(self.norm, dict) else None
+    if not isinstance(eps, (int, float)) or isinstance(eps, bool) or not eps > 0:
+      raise ConfigError(f"norm.eps must be a positive number, got {eps!r}")
+    for key in ("residual_mult", "logit_scale"):
+      v = getattr(self, key)
+      if not isinstance(v, (int, float)) or isinstance(v, bool):
+        raise ConfigError(f"{key} must be a number, got {v!r}")
+    if not self.layers:
+      raise ConfigError("layers must list at least one layer")
+    for i in range(len(self.layers)):
+      self.weights_layer(i)
+      self.mixer_of(i)
+      self.mlp_of(i)
+
+  @property
+  def norm_eps(self) -> float:
+    return float(self.norm["eps"])
+
+  def weights_layer(self, i: int) -> int:
+    """The layer whose tensors layer ``i`` runs: itself, or the one its ``weights_of`` names (which has tensors of its own or
+    names a third in turn).  The rest of a sharing layer's entry must equal the other's."""
+    seen = [i]
+    while self.layers[seen[-1]].get("weights_of") is not None:
+      j = self.layers[seen[-1]]["weights_of"]
+      if not isinstance(j, int) or isinstance(j, bool) or not (0 <= j < len(self.layers)) or j in seen:
+        raise ConfigError(f"layers[{seen[-1]}].weights_of={j!r} must name another layer (0..{len(self.layers) - 1}) and not come back to itself")
+      seen.append(j)
+    src = seen[-1]
+    if src != i:
+      mine = {k: v for k, v in self.layers[i].items() if k != "weights_of"}
+      theirs = {k: v for k, v in self.layers[src].items() if k != "weights_of"}
+      if mine != theirs:
+        raise ConfigError(f"layers[{i}] runs the weights of layers[{src}] but its entry differs from that layer's")
+    return src
+
+  def type_of(self, i: int) -> str:
+    kind = self.layers[i].get("type")
+    if kind not in self.TYPES:
+      raise ConfigError(f"layers[{i}].type={kind!r} is not a mixer of this design (known: {', '.join(self.TYPES)})")
+    return kind
+
+  def mixer_of(self, i: int):
+    """The typed mixer configuration of layer ``i``: a ``SigmoidAttentionConfig``, an ``RglruConfig`` or a ``MinGruConfig``."""
+    kind = self.type_of(i)
+    m = self.layers[i].get("mixer")
+    where = f"layers[{i}].mixer"
+    if not isinstance(m, dict):
+      raise ConfigError(f"{where} is missing")
+    if kind == "rglru":
+      c = RglruConfig(*(_positive_int(m, k, where) for k in ("width", "blocks", "conv")))
+      if c.width % c.blocks:
+        raise ConfigError(f"{where}.width={c.width} must be a multiple of blocks={c.blocks}")
+      return c
+    if kind == "mingru":
+      return MinGruConfig(_positive_int(m, "width", where))
+    cap = m.get("softcap")
+    if cap is not None and (not isinstance(cap, (int, float)) or isinstance(cap, bool) or not cap > 0):
+      raise ConfigError(f"{where}.softcap must be a positive number or absent, got {cap!r}")
+    c = SigmoidAttentionConfig(*(_positive_int(m, k, where) for k in ("heads", "kv_heads", "dim", "vdim")), _number(m, "scale", where),
+                               float(cap) if cap is not None else None, RotationConfig.read(m, where, ()))
+    if c.heads % c.kv_heads:
+      raise ConfigError(f"{where}.heads={c.heads} must be a multiple of kv_heads={c.kv_heads}")
+    if c.rot.dims > c.dim:
+      raise ConfigError(f"{where}.rot.dims={c.rot.dims} is more than dim={c.dim}")
+    return c
+
+  def mlp_of(self, i: int) -> Optional[ClampedMoeConfig]:
+    mlp = self.layers[i].get("mlp")
+    if mlp is None:
+      return None
+    where = f"layers[{i}].mlp"
+    if not isinstance(mlp, dict) or mlp.get("kind") != "moe":
+      raise ConfigError(f"{where}.kind={mlp.get('kind') if isinstance(mlp, dict) else mlp!r} is not known (moe)")
+    expert, router, shared = mlp.get("expert"), mlp.get("router"), mlp.get("shared")
+    if not isinstance(expert, dict) or not isinstance(router, dict):
+      raise ConfigError(f"{where} needs 'expert' and 'router'")
+    sc = None
+    if shared is not None:
+      if not isinstance(shared, dict):
+        raise ConfigError(f"{where}.shared must be an object or absent")
+      sc = SharedExpertConfig(_positive_int(shared, "ff", where + ".shared"), _number(shared, "limit", where + ".shared"))
+    c = ClampedMoeConfig(_positive_int(expert, "ff", where + ".expert"), _number(expert, "limit", where + ".expert"),
+                         _positive_int(router, "experts", where + ".router"), _positive_int(router, "top", where + ".router"), sc)
+    if c.top > c.experts:
+      raise ConfigError(f"{where}.router.top={c.top} is more than experts={c.experts}")
+    return c
+
+  def to_dict(self) -> Dict[str, Any]:
+    d = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width, "norm": dict(self.norm),
+         "residual_mult": self.residual_mult, "logit_scale": self.logit_scale, "layers": [dict(x) for x in self.layers]}
+    d.update(self.extra)
+    return d

@@ -1,4 +1,5 @@
-// Activations of the feed-forwards.  SwiGLU: out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu in float32, one rounding
+// Activations of the feed-forwards.  Gated: out[t, i] = act(gu[t, i]) * gu[t, I + i] - SwiGLU, silu(g) * u, or the clamped
+// form of common.cuh (MiGlu) - in float32, one rounding
 // (bfloat16: with the hardware's exponential and reciprocal; float32: exact division and expf).
 // Stands where the reference runs a Triton kernel (kernels/triton/silu_mul.py:6-42).
 #include "common.cuh"
@@ -6,7 +7,7 @@
 namespace {
 
 template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int I, size_t total) {
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int I, size_t total, int kind, float limit) {
   mi::grid_dependency_sync();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
@@ -14,12 +15,12 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, i
     const int i = (int)(idx - t * I);
     const float g = mi::to_float(gu[t * 2 * I + i]);
     const float u = mi::to_float(gu[t * 2 * I + I + i]);
-    out[idx] = mi::from_float<T>(sizeof(T) == 4 ? mi::silu_mul_exact(g, u) : mi::silu_mul_fast(g, u));
+    out[idx] = mi::from_float<T>(sizeof(T) == 4 ? mi::glu_exact(g, u, kind, limit) : mi::glu_fast(g, u, kind, limit));
   }
 }
 
 // bf16 with I a multiple of 8: 16-byte loads and stores.
-__global__ void silu_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu, int I8, size_t total8) {
+__global__ void silu_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu, int I8, size_t total8, int kind, float limit) {
   mi::grid_dependency_sync();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I8;
@@ -33,7 +34,7 @@ __global__ void silu_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const float2 a = __bfloat1622float2(gp[k]), b = __bfloat1622float2(up[k]);
-      rp[k] = __floats2bfloat162_rn(mi::silu_mul_fast(a.x, b.x), mi::silu_mul_fast(a.y, b.y));
+      rp[k] = __floats2bfloat162_rn(mi::glu_fast(a.x, b.x, kind, limit), mi::glu_fast(a.y, b.y, kind, limit));
     }
     *reinterpret_cast<uint4*>(out + idx * 8) = r;
   }
@@ -89,8 +90,10 @@ MI_API int mi_relu_squared(void* out, const void* x, int dtype, long long n, cud
   return 0;
 }
 
-MI_API int mi_silu_mul(void* out, const void* gu, int dtype, int T, int I, cudaStream_t stream) {
-  MI_REQUIRE(T >= 0 && I > 0, "silu_mul: bad sizes T=%d I=%d", T, I);
+// kind: a MiGlu; limit: the clamp of MI_GLU_CLAMPED.
+MI_API int mi_glu_mul(void* out, const void* gu, int dtype, int T, int I, int kind, float limit, cudaStream_t stream) {
+  MI_REQUIRE(T >= 0 && I > 0, "glu_mul: bad sizes T=%d I=%d", T, I);
+  MI_REQUIRE(kind == MI_GLU_SILU || (kind == MI_GLU_CLAMPED && limit > 0.f), "glu_mul: unknown kind %d or a limit that is not positive", kind);
   if (T == 0) return 0;
   const size_t total = (size_t)T * I;
   const int threads = 256;
@@ -99,13 +102,17 @@ MI_API int mi_silu_mul(void* out, const void* gu, int dtype, int T, int I, cudaS
   if (dtype == MI_BF16 && I % 8 == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)gu % 16) == 0) {
     const size_t total8 = total / 8;
     const int b8 = (int)((total8 + threads - 1) / threads < most ? (total8 + threads - 1) / threads : most);
-    mi::launch(silu_mul_bf16x8_kernel, dim3(b8), dim3(threads), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I / 8, total8);
+    mi::launch(silu_mul_bf16x8_kernel, dim3(b8), dim3(threads), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I / 8, total8, kind, limit);
   } else if (dtype == MI_BF16)
-    mi::launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I, total);
+    mi::launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I, total, kind, limit);
   else if (dtype == MI_F32)
-    mi::launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)out, (const float*)gu, I, total);
+    mi::launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)out, (const float*)gu, I, total, kind, limit);
   else
-    return mi_fail("silu_mul: unknown dtype %d", dtype);
-  MI_LAUNCH_OK("silu_mul");
+    return mi_fail("glu_mul: unknown dtype %d", dtype);
+  MI_LAUNCH_OK("glu_mul");
   return 0;
+}
+
+MI_API int mi_silu_mul(void* out, const void* gu, int dtype, int T, int I, cudaStream_t stream) {
+  return mi_glu_mul(out, gu, dtype, T, I, MI_GLU_SILU, 0.f, stream);
 }

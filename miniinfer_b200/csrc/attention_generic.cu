@@ -21,6 +21,11 @@
 // element by element with sigmoid(gate[token, head, :]); and out_hd < head_dim - only the first out_hd
 // values of a head are written (the cache rows are padded).  With a window, keep_first > 0 lets every token also see
 // the first keep_first keys of its request, at their true positions.
+//
+// Two more, for designs that shape the scores: softcap > 0 replaces a scaled score s by softcap * tanh(s / softcap) before
+// anything else sees it; and with score_bias (one float per query head) the weights are not a softmax at all - the weight
+// of a visible key is sigmoid(s + score_bias[head]), nothing is normalised over the keys, and the output is the plain sum
+// of the weighted values (a sink has no meaning then).
 #include "common.cuh"
 
 namespace {
@@ -67,7 +72,7 @@ attention_generic_kernel(T* __restrict__ out, const T* __restrict__ q_base, int 
                          const int* __restrict__ token_item, const int* __restrict__ positions,
                          const int* __restrict__ seq_slot, int nh, int nkv, int hd, int page_size,
                          float scale, int window, const float* __restrict__ sink, const T* __restrict__ gate,
-                         int gate_stride, int out_hd, int keep_first) {
+                         int gate_stride, int out_hd, int keep_first, float softcap, const float* __restrict__ score_bias) {
   mi::grid_dependency_sync();
   __shared__ float qs[WARPS][MAX_HD];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -93,6 +98,9 @@ attention_generic_kernel(T* __restrict__ out, const T* __restrict__ q_base, int 
   for (int i = 0; i < MAX_HD / 32; ++i) o[i] = 0.f;
   float m = -INFINITY, l = 0.f;
   if (sink) { m = sink[head]; l = 1.f; }
+  const bool unnormalised = score_bias != nullptr;
+  const float sb = unnormalised ? score_bias[head] : 0.f;
+  if (unnormalised) m = 0.f;
 
   // two stretches of keys: the request's first keep_first keys that the window has passed (none without a window),
   // then the window itself; each in chunks of 32 aligned to multiples of 32
@@ -107,14 +115,20 @@ attention_generic_kernel(T* __restrict__ out, const T* __restrict__ q_base, int 
       const int page = bt[j / page_size];
       koff = (long long)((size_t)page * page_elems + head_off + (size_t)(j % page_size) * hd);
       s = scale * dot_row<T>(kv_layer + koff, qs[warp], hd);
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
     }
-    const float m_new = fmaxf(m, mi::warp_max(s));
-    const float alpha = expf(m - m_new);
-    const float pe = valid ? expf(s - m_new) : 0.f;
-    l = l * alpha + mi::warp_sum(pe);
-    m = m_new;
+    float pe;
+    if (unnormalised) {
+      pe = valid ? 1.f / (1.f + expf(-(s + sb))) : 0.f;
+    } else {
+      const float m_new = fmaxf(m, mi::warp_max(s));
+      const float alpha = expf(m - m_new);
+      pe = valid ? expf(s - m_new) : 0.f;
+      l = l * alpha + mi::warp_sum(pe);
+      m = m_new;
 #pragma unroll
-    for (int i = 0; i < MAX_HD / 32; ++i) o[i] *= alpha;
+      for (int i = 0; i < MAX_HD / 32; ++i) o[i] *= alpha;
+    }
     for (int jj = 0; jj < 32; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, pe, jj);
       const long long off = __shfl_sync(0xffffffffu, koff, jj);
@@ -127,7 +141,7 @@ attention_generic_kernel(T* __restrict__ out, const T* __restrict__ q_base, int 
       }
     }
   }
-  const float inv = 1.f / l;
+  const float inv = unnormalised ? 1.f : 1.f / l;
   T* dst = out + ((size_t)tkn * nh + head) * out_hd;
   const T* gt = gate ? gate + (size_t)tkn * gate_stride + (size_t)head * out_hd : nullptr;
 #pragma unroll
@@ -148,7 +162,8 @@ MI_API int mi_attention_generic(void* out, const void* q_base, int q_stride, int
                                 const int* block_table, int bt_stride, const int* token_item,
                                 const int* positions, const int* seq_slot, int T, int nh, int nkv, int hd,
                                 int page_size, float scale, int window, const float* sink, const void* gate,
-                                int gate_stride, int out_hd, int keep_first, cudaStream_t stream) {
+                                int gate_stride, int out_hd, int keep_first, float softcap, const float* score_bias, cudaStream_t stream) {
+  MI_REQUIRE(!(softcap < 0.f) && !(sink && score_bias), "attention: softcap=%f must not be negative, and unnormalised weights take no sink", softcap);
   MI_REQUIRE(keep_first >= 0, "attention: keep_first=%d must not be negative", keep_first);
   MI_REQUIRE(out_hd > 0 && out_hd <= hd, "attention: out_hd=%d must lie in 1..head_dim", out_hd);
   MI_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention: bad head counts nh=%d nkv=%d", nh, nkv);
@@ -161,11 +176,11 @@ MI_API int mi_attention_generic(void* out, const void* q_base, int q_stride, int
     mi::launch(attention_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(WARPS * 32), 0, stream, 
         (__nv_bfloat16*)out, (const __nv_bfloat16*)q_base, q_stride, (const __nv_bfloat16*)kv_layer, block_table,
         bt_stride, token_item, positions, seq_slot, nh, nkv, hd, page_size, scale, window, sink, (const __nv_bfloat16*)gate,
-        gate_stride, out_hd, keep_first);
+        gate_stride, out_hd, keep_first, softcap, score_bias);
   else if (dtype == MI_F32)
     mi::launch(attention_generic_kernel<float>, dim3(grid), dim3(WARPS * 32), 0, stream, 
         (float*)out, (const float*)q_base, q_stride, (const float*)kv_layer, block_table, bt_stride, token_item,
-        positions, seq_slot, nh, nkv, hd, page_size, scale, window, sink, (const float*)gate, gate_stride, out_hd, keep_first);
+        positions, seq_slot, nh, nkv, hd, page_size, scale, window, sink, (const float*)gate, gate_stride, out_hd, keep_first, softcap, score_bias);
   else
     return mi_fail("attention: unknown dtype %d", dtype);
   MI_LAUNCH_OK("attention_generic");

@@ -18,6 +18,7 @@
 #define MI_API extern "C" __attribute__((visibility("default")))
 
 enum MiDtype { MI_F32 = 0, MI_BF16 = 1 };
+enum MiGlu { MI_GLU_SILU = 0, MI_GLU_CLAMPED = 1 };   // gated activations: see mi::glu_fast
 
 inline thread_local char mi_error_text[1024] = "";
 
@@ -102,6 +103,27 @@ __device__ __forceinline__ void grid_dependency_sync() {
 // two-kernel path agree bit for bit on the same products; the float32 path divides exactly.
 __device__ __forceinline__ float silu_mul_fast(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 __device__ __forceinline__ float silu_mul_exact(float g, float u) { return g / (1.f + expf(-g)) * u; }
+
+// The gated activations of the feed-forwards, act(g) * u from a gate value g and an up value u (MiGlu):
+//   MI_GLU_SILU     silu(g) * u
+//   MI_GLU_CLAMPED  with a limit L: g' = min(g, L), u' = clamp(u, -L, L); g' * sigmoid(1.702 g') * (u' + 1)
+// `fast` forms for the bfloat16 paths (hardware exponential and reciprocal), `exact` ones for float32.
+__device__ __forceinline__ float glu_fast(float g, float u, int kind, float limit) {
+  if (kind == MI_GLU_CLAMPED) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return __fdividef(g, 1.f + __expf(-1.702f * g)) * (u + 1.f);
+  }
+  return silu_mul_fast(g, u);
+}
+__device__ __forceinline__ float glu_exact(float g, float u, int kind, float limit) {
+  if (kind == MI_GLU_CLAMPED) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+  }
+  return silu_mul_exact(g, u);
+}
 
 __device__ __forceinline__ float to_float(float x) { return x; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }

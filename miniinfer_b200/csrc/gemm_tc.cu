@@ -77,6 +77,8 @@ struct Args {
   const int* tile_expert;
   int tile_rows, expert_rows;
   int act;               // plain product only: 1 - out = max(bf16(product), 0)^2, the squared ReLU of a feed-forward; 0 - the product
+  int glu;               // gate-and-up product only: the gated activation (a MiGlu of common.cuh) and its limit
+  float limit;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -370,7 +372,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const float gg = round_bf16(g[i]), uu = round_bf16(u[i]);
-            g[i] = mi::silu_mul_fast(gg, uu);
+            g[i] = mi::glu_fast(gg, uu, a.glu, a.limit);
           }
         } else if (a.act == 1) {
           // the values the product followed by the activation kernel leaves: rounded, clamped, squared
@@ -497,7 +499,7 @@ int launch_tc(const CUtensorMap& xm, const CUtensorMap& wm, const Args& a, int s
 
 template <bool SWIGLU, bool GROUPED = false>
 int run(void* out, const void* x, const void* w, int M, int N, int K, int ldo, int* status, int pairs, cudaStream_t stream,
-        int experts = 1, const int* tile_expert = nullptr, int tile_rows = 0, int act = 0) {
+        int experts = 1, const int* tile_expert = nullptr, int tile_rows = 0, int act = 0, int glu = MI_GLU_SILU, float limit = 0.f) {
   // N: output columns; w has N rows (plain) or 2 N rows (SwiGLU), per expert
   MI_REQUIRE(M > 0 && N > 0 && K >= BK && K % 8 == 0 && N % 8 == 0 && ldo % 8 == 0 && ldo >= N,
              "gemm_tc: M=%d N=%d K=%d ldo=%d: K (at least 64), N and the row stride must be multiples of 8", M, N, K, ldo);
@@ -509,6 +511,7 @@ int run(void* out, const void* x, const void* w, int M, int N, int K, int ldo, i
   a.tile_expert = tile_expert;
   a.tile_rows = tile_rows;
   a.act = SWIGLU ? 0 : act;
+  a.glu = glu; a.limit = limit;
   a.expert_rows = SWIGLU ? 2 * N : N;
   a.out = (__nv_bfloat16*)out;
   a.status = status;
@@ -540,14 +543,23 @@ MI_API int mi_gemm_tc_swiglu_bf16(void* out, const void* x, const void* w, int M
   return run<true>(out, x, w, M, I, K, ldo, status, pairs, stream);
 }
 
+// The same with another gated activation (a MiGlu of common.cuh) in the epilogue.
+MI_API int mi_gemm_tc_glu_bf16(void* out, const void* x, const void* w, int M, int I, int K, int ldo, int* status,
+                               int pairs, int glu, float limit, cudaStream_t stream) {
+  MI_REQUIRE(glu == MI_GLU_SILU || (glu == MI_GLU_CLAMPED && limit > 0.f), "gemm_tc_glu: unknown activation %d or a limit that is not positive", glu);
+  return run<true>(out, x, w, M, I, K, ldo, status, pairs, stream, 1, nullptr, 0, 0, glu, limit);
+}
+
 // The grouped form: x [M, K] holds rows sorted by expert, every expert's rows starting at a multiple of tile_rows (a
 // multiple of 256); tile_expert [M / tile_rows] (device) names the expert of each stretch, -1 where nobody owns the rows;
 // w stacks the experts' matrices ([experts, 2 N, K] with SwiGLU, gate rows then up rows; [experts, N, K] without).
+// glu, limit: the gated activation of the SwiGLU form (a MiGlu of common.cuh).
 MI_API int mi_gemm_tc_grouped_bf16(void* out, const void* x, const void* w, int M, int N, int K, int ldo, int experts, int swiglu,
-                                   const int* tile_expert, int tile_rows, int* status, int pairs, cudaStream_t stream) {
+                                   const int* tile_expert, int tile_rows, int* status, int pairs, int glu, float limit, cudaStream_t stream) {
+  MI_REQUIRE(glu == MI_GLU_SILU || (glu == MI_GLU_CLAMPED && limit > 0.f), "gemm_tc_grouped: unknown activation %d or a limit that is not positive", glu);
   MI_REQUIRE(experts > 0 && tile_expert != nullptr && tile_rows > 0 && tile_rows % 256 == 0 && M % tile_rows == 0,
              "gemm_tc_grouped: rows=%d must come in stretches of tile_rows=%d, a multiple of 256", M, tile_rows);
-  return swiglu ? run<true, true>(out, x, w, M, N, K, ldo, status, pairs, stream, experts, tile_expert, tile_rows)
+  return swiglu ? run<true, true>(out, x, w, M, N, K, ldo, status, pairs, stream, experts, tile_expert, tile_rows, 0, glu, limit)
                 : run<false, true>(out, x, w, M, N, K, ldo, status, pairs, stream, experts, tile_expert, tile_rows);
 }
 

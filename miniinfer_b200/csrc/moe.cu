@@ -4,7 +4,8 @@
 //   route    (the logits z = W_router h come from the engine's matrix product, accumulated in float32; bfloat16 operands
 //            multiply exactly in float32, so this is the 32-bit sum of the rounded inputs.)  One warp per token: scores
 //            s = sigmoid(z), choice = s + correction; the `top` experts of largest choice (ties: the lower
-//            index); weights = their s divided by (the sum of those s + 1e-20).
+//            index); weights = their s divided by (the sum of those s + 1e-20).  Or (mode 1) the `top` largest logits
+//            are chosen and the weights are the softmax over the chosen logits alone.
 //   align    one block: counts the (token, choice) pairs of every expert, gives each expert a range of
 //            rows rounded up to the row tile, and every pair a row in its expert's range.  Rows nobody
 //            owns are marked -1, tiles nobody owns too; the grid of the products is sized for the worst case.
@@ -27,24 +28,26 @@ constexpr int ROUTE_WARPS = 8;
 // A warp per token: a lane keeps the scores of the experts lane, lane + 32, ... (up to eight) and the warp picks the
 // `top` largest choices one after the other.
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
-moe_route_kernel(const float* __restrict__ z, int Tn, const float* __restrict__ corr, int E, int top,
+moe_route_kernel(const float* __restrict__ z, int z_stride, int Tn, const float* __restrict__ corr, int E, int top, int mode,
                  int* __restrict__ idx_out, float* __restrict__ w_out) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.x * ROUTE_WARPS + warp;
   float c_fix[MAX_EXPERTS / 32];
 #pragma unroll
-  for (int i = 0; i < MAX_EXPERTS / 32; ++i) c_fix[i] = lane + 32 * i < E ? corr[lane + 32 * i] : 0.f;   // a weight: fetched before the wait
+  for (int i = 0; i < MAX_EXPERTS / 32; ++i) c_fix[i] = (corr && lane + 32 * i < E) ? corr[lane + 32 * i] : 0.f;   // a weight: fetched before the wait
   mi::grid_dependency_sync();
   if (t >= Tn) return;
   float score[MAX_EXPERTS / 32], choice[MAX_EXPERTS / 32];
 #pragma unroll
   for (int i = 0; i < MAX_EXPERTS / 32; ++i) {
     const int e = lane + 32 * i;
-    score[i] = e < E ? 1.f / (1.f + expf(-z[(size_t)t * E + e])) : 0.f;
+    const float ze = e < E ? z[(size_t)t * z_stride + e] : 0.f;
+    score[i] = e < E ? (mode == 1 ? ze : 1.f / (1.f + expf(-ze))) : 0.f;
     choice[i] = e < E ? score[i] + c_fix[i] : -INFINITY;
   }
   float sum = 0.f;
   float mine = 0.f;   // lane k keeps the score of choice k
+  float first = 0.f;  // mode 1: the largest logit, which is the first choice
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY, best_s = 0.f;
     int bi = 0x7fffffff;
@@ -58,6 +61,10 @@ moe_route_kernel(const float* __restrict__ z, int Tn, const float* __restrict__ 
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; best_s = os; }
     }
+    if (mode == 1) {
+      if (k == 0) first = best_s;
+      best_s = expf(best_s - first);
+    }
     sum += best_s;
     if (lane == k) mine = best_s;
     if (lane == 0) idx_out[(size_t)t * top + k] = bi;
@@ -65,7 +72,7 @@ moe_route_kernel(const float* __restrict__ z, int Tn, const float* __restrict__ 
     for (int i = 0; i < MAX_EXPERTS / 32; ++i)
       if (lane + 32 * i == bi) choice[i] = -INFINITY;
   }
-  if (lane < top) w_out[(size_t)t * top + lane] = mine / (sum + 1e-20f);
+  if (lane < top) w_out[(size_t)t * top + lane] = mode == 1 ? mine / sum : mine / (sum + 1e-20f);
 }
 
 __global__ void __launch_bounds__(1024)
@@ -145,6 +152,8 @@ struct GroupedArgs {
   const int* tile_expert;
   int N, K, top, gather;
   long long w_expert_stride;   // elements between two experts' matrices
+  int glu;                     // the gated activation of the gate-and-up product (a MiGlu) and its limit
+  float limit;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -271,8 +280,8 @@ moe_gemm_bf16_kernel(GroupedArgs a) {
       const int n = n0 + wn * WN_COLS + i * 8 + 2 * t;
       if (n >= N) continue;
       if (SWIGLU) {
-        const float y0 = mi::silu_mul_fast(acc[0][i][2 * h], acc[1][i][2 * h]);
-        const float y1 = mi::silu_mul_fast(acc[0][i][2 * h + 1], acc[1][i][2 * h + 1]);
+        const float y0 = mi::glu_fast(acc[0][i][2 * h], acc[1][i][2 * h], a.glu, a.limit);
+        const float y1 = mi::glu_fast(acc[0][i][2 * h + 1], acc[1][i][2 * h + 1], a.glu, a.limit);
         __nv_bfloat16* o = (__nv_bfloat16*)a.out + orow + n;
         o[0] = __float2bfloat16_rn(y0);
         if (n + 1 < N) o[1] = __float2bfloat16_rn(y1);
@@ -382,7 +391,7 @@ moe_stream_bf16_kernel(GroupedArgs a) {
       for (int k = 0; k < KS; ++k) v[b] += red[grp * KS + k][r][b * 8 + c];
     }
     const size_t o = (size_t)(tile * 16 + r) * N + n;
-    if (SWIGLU) ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(mi::silu_mul_fast(v[0], v[NB - 1]));
+    if (SWIGLU) ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(mi::glu_fast(v[0], v[NB - 1], a.glu, a.limit));
     else ((float*)a.out)[o] = v[0];
   }
 }
@@ -443,19 +452,23 @@ moe_gemm_f32_kernel(GroupedArgs a) {
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     const int n = n0 + cg * 4 + c;
-    if (n < N) o[n] = SWIGLU ? mi::silu_mul_exact(acc[0][c], acc[NB - 1][c]) : acc[0][c];
+    if (n < N) o[n] = SWIGLU ? mi::glu_exact(acc[0][c], acc[NB - 1][c], a.glu, a.limit) : acc[0][c];
   }
 }
 
 template <typename TOut, typename TY>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(TOut* __restrict__ out, const TY* __restrict__ y, const int* __restrict__ pos_of,
-                   const float* __restrict__ w, int top, int N) {
+                   const float* __restrict__ w, int top, int N, const TOut* __restrict__ shared,
+                   const float* __restrict__ shared_logit, int logit_stride) {
   mi::grid_dependency_sync();
   const int t = blockIdx.x;
+  // an expert every token runs through: its row joins the sum, times the sigmoid of the token's gate logit if there is one
+  const float sw = shared ? (shared_logit ? 1.f / (1.f + expf(-shared_logit[(size_t)t * logit_stride])) : 1.f) : 0.f;
   for (int n = threadIdx.x; n < N; n += blockDim.x) {
     float acc = 0.f;
     for (int k = 0; k < top; ++k) acc = fmaf(w[(size_t)t * top + k], mi::to_float(y[(size_t)pos_of[(size_t)t * top + k] * N + n]), acc);
+    if (shared) acc = fmaf(sw, mi::to_float(shared[(size_t)t * N + n]), acc);
     out[(size_t)t * N + n] = mi::from_float<TOut>(acc);
   }
 }
@@ -495,12 +508,16 @@ MI_API int mi_moe_row_tile(int n_pairs, int E, int dtype) {
   return n_pairs >= 32 * E ? 64 : 16;
 }
 
-// z: the router's logits [T, E] in float32 (a product of the engine's own: W_router h with float32 accumulation)
-MI_API int mi_moe_route(const float* z, int T, const float* correction, int E, int top, int* idx_out, float* w_out, cudaStream_t stream) {
+// z: the router's logits in float32, rows of z_stride >= E values (a product of the engine's own: W_router h with float32
+// accumulation).  mode 0: sigmoid scores, chosen by score + correction, weights the scores over their sum; mode 1: the
+// largest logits are chosen (correction, if given, added for the choice), weights the softmax over the chosen logits.
+MI_API int mi_moe_route(const float* z, int z_stride, int T, const float* correction, int E, int top, int mode, int* idx_out, float* w_out,
+                        cudaStream_t stream) {
+  MI_REQUIRE((mode == 0 || mode == 1) && z_stride >= E, "moe_route: mode %d is not known or rows of %d logits are too short", mode, z_stride);
   MI_REQUIRE(T >= 0 && E > 0 && E <= MAX_EXPERTS, "moe_route: experts=%d must lie in 1..%d", E, MAX_EXPERTS);
   MI_REQUIRE(top > 0 && top <= E && top <= 32, "moe_route: top=%d must lie in 1..min(experts, 32)", top);
   if (T == 0) return 0;
-  mi::launch(moe_route_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), 0, stream, z, T, correction, E, top, idx_out, w_out);
+  mi::launch(moe_route_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), 0, stream, z, z_stride, T, correction, E, top, mode, idx_out, w_out);
   MI_LAUNCH_OK("moe_route");
   return 0;
 }
@@ -518,15 +535,18 @@ MI_API int mi_moe_align(const int* topk_idx, int n_pairs, int E, int TM, int* so
   return 0;
 }
 
-// swiglu 1: out[row, :N] = silu(a w_gate^T) * (a w_up^T), the expert's matrix holding N gate rows and then N up rows,
-// rows gathered from the tokens; swiglu 0: out[row, :N] = a w^T in float32, rows by position.
+// swiglu 1: out[row, :N] = act(a w_gate^T) * (a w_up^T), the expert's matrix holding N gate rows and then N up rows,
+// rows gathered from the tokens, the gated activation `glu` (a MiGlu) with its `limit`; swiglu 0: out[row, :N] = a w^T in
+// float32, rows by position.
 MI_API int mi_moe_gemm(const void* a_rows, int dtype, int a_stride, const void* w, void* out, const int* sorted_pair,
-                       const int* tile_expert, int max_tiles, int TM, int N, int K, int top, int swiglu, cudaStream_t stream) {
+                       const int* tile_expert, int max_tiles, int TM, int N, int K, int top, int swiglu, int glu, float limit,
+                       cudaStream_t stream) {
+  MI_REQUIRE(glu == MI_GLU_SILU || (glu == MI_GLU_CLAMPED && limit > 0.f), "moe_gemm: unknown activation %d or a limit that is not positive", glu);
   MI_REQUIRE(N > 0 && K > 0 && max_tiles >= 0 && max_tiles <= 65535, "moe_gemm: bad sizes N=%d K=%d tiles=%d", N, K, max_tiles);
   if (max_tiles == 0) return 0;
   GroupedArgs g;
   g.a = a_rows; g.a_stride = a_stride; g.w = w; g.out = out; g.sorted_pair = sorted_pair; g.tile_expert = tile_expert;
-  g.N = N; g.K = K; g.top = top; g.gather = swiglu ? 1 : 0;
+  g.N = N; g.K = K; g.top = top; g.gather = swiglu ? 1 : 0; g.glu = glu; g.limit = limit;
   g.w_expert_stride = (long long)(swiglu ? 2 : 1) * N * K;
   if (dtype == MI_F32) {
     MI_REQUIRE(TM == FTM, "moe_gemm: the float32 product takes row tiles of %d", FTM);
@@ -571,17 +591,18 @@ MI_API int mi_moe_gather(void* xs, const void* x, const int* sorted_pair, int ro
   return 0;
 }
 
-// y: the down rows, float32 (y_dtype MI_F32) or bfloat16
+// y: the down rows, float32 (y_dtype MI_F32) or bfloat16.  shared (or null): rows [T, N] of out's type that every token adds,
+// times sigmoid(shared_logit[t * logit_stride]) if shared_logit is given.
 MI_API int mi_moe_combine(void* out, int out_dtype, const void* y, int y_dtype, const int* pos_of, const float* weights, int T, int top, int N,
-                          cudaStream_t stream) {
+                          const void* shared, const float* shared_logit, int logit_stride, cudaStream_t stream) {
   MI_REQUIRE(T >= 0 && top > 0 && N > 0, "moe_combine: bad sizes");
   if (T == 0) return 0;
   if (out_dtype == MI_BF16 && y_dtype == MI_F32)
-    mi::launch(moe_combine_kernel<__nv_bfloat16, float>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)out, (const float*)y, pos_of, weights, top, N);
+    mi::launch(moe_combine_kernel<__nv_bfloat16, float>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)out, (const float*)y, pos_of, weights, top, N, (const __nv_bfloat16*)shared, shared_logit, logit_stride);
   else if (out_dtype == MI_BF16 && y_dtype == MI_BF16)
-    mi::launch(moe_combine_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)y, pos_of, weights, top, N);
+    mi::launch(moe_combine_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)y, pos_of, weights, top, N, (const __nv_bfloat16*)shared, shared_logit, logit_stride);
   else if (out_dtype == MI_F32 && y_dtype == MI_F32)
-    mi::launch(moe_combine_kernel<float, float>, dim3(T), dim3(256), 0, stream, (float*)out, (const float*)y, pos_of, weights, top, N);
+    mi::launch(moe_combine_kernel<float, float>, dim3(T), dim3(256), 0, stream, (float*)out, (const float*)y, pos_of, weights, top, N, (const float*)shared, shared_logit, logit_stride);
   else
     return mi_fail("moe_combine: unknown dtypes %d, %d", out_dtype, y_dtype);
   MI_LAUNCH_OK("moe_combine");

@@ -20,13 +20,14 @@ __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); 
 // ------------------------------------------------------------------------------------------------------------
 // Short causal convolution over time, per channel: out[t, c] = act(bias[c] + sum_k w[c, taps - 1 - k] * in[t - k, c]),
 // the inputs before the step's first token coming from the item's state (the last taps - 1 inputs of the request,
-// oldest first, zeros before its start).  A thread per (token, channel).
+// oldest first, zeros before its start).  With in_bias, in[t, c] = x[t, c] + in_bias[c] (the bias of the projection that
+// made x; the zeros before a request's start stay zeros), and the state keeps the inputs with it.  A thread per (token, channel).
 constexpr int MAX_TAPS = 16;
 
 template <typename T>
 __global__ void __launch_bounds__(256)
 causal_conv_kernel(T* __restrict__ out, int ldo, const T* __restrict__ x, int ldx, const float* __restrict__ w,
-                   const float* __restrict__ bias, const float* __restrict__ state, long long state_stride,
+                   const float* __restrict__ bias, const float* __restrict__ in_bias, const float* __restrict__ state, long long state_stride,
                    const int* __restrict__ token_item, const int* __restrict__ q_start, const int* __restrict__ seq_slot,
                    int C, int taps, int silu) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -38,9 +39,10 @@ causal_conv_kernel(T* __restrict__ out, int ldo, const T* __restrict__ x, int ld
   if (c >= C) return;
   const float* st = state + (size_t)slot * state_stride;   // [taps - 1][C]
   float acc = bias ? bias[c] : 0.f;
+  const float ib = in_bias ? in_bias[c] : 0.f;
   for (int k = taps - 1; k >= 0; --k) {                    // oldest input first
     const int jj = j - k;
-    const float v = jj >= 0 ? mi::to_float(x[(size_t)(t - k) * ldx + c]) : st[(size_t)(taps - 1 + jj) * C + c];
+    const float v = jj >= 0 ? mi::to_float(x[(size_t)(t - k) * ldx + c]) + ib : st[(size_t)(taps - 1 + jj) * C + c];
     acc = fmaf(w[(size_t)c * taps + (taps - 1 - k)], v, acc);
   }
   if (silu) acc = silu_f(acc);
@@ -50,7 +52,7 @@ causal_conv_kernel(T* __restrict__ out, int ldo, const T* __restrict__ x, int ld
 // After the convolution has run: the state becomes the last taps - 1 inputs of the request.  A thread per (item, channel).
 template <typename T>
 __global__ void __launch_bounds__(256)
-conv_state_kernel(float* __restrict__ state, long long state_stride, const T* __restrict__ x, int ldx,
+conv_state_kernel(float* __restrict__ state, long long state_stride, const T* __restrict__ x, int ldx, const float* __restrict__ in_bias,
                   const int* __restrict__ q_start, const int* __restrict__ q_len, const int* __restrict__ seq_slot,
                   int C, int taps) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -61,11 +63,12 @@ conv_state_kernel(float* __restrict__ state, long long state_stride, const T* __
   float* st = state + (size_t)slot * state_stride;
   float keep[MAX_TAPS];
   const int S = taps - 1;
+  const float ib = in_bias ? in_bias[c] : 0.f;
 #pragma unroll
   for (int r = 0; r < MAX_TAPS; ++r) {
     if (r >= S) break;
     const int jj = n - S + r;                               // index among the new tokens; negative: an older input
-    keep[r] = jj >= 0 ? mi::to_float(x[(size_t)(row0 + jj) * ldx + c]) : st[(size_t)(S + jj) * C + c];
+    keep[r] = jj >= 0 ? mi::to_float(x[(size_t)(row0 + jj) * ldx + c]) + ib : st[(size_t)(S + jj) * C + c];
   }
 #pragma unroll
   for (int r = 0; r < MAX_TAPS; ++r) {
@@ -566,7 +569,7 @@ delta_output_kernel(T* __restrict__ out, int ldo, const float* __restrict__ raw,
 
 }  // namespace
 
-MI_API int mi_causal_conv(void* out, int ldo, const void* x, int ldx, int dtype, const float* w, const float* bias,
+MI_API int mi_causal_conv(void* out, int ldo, const void* x, int ldx, int dtype, const float* w, const float* bias, const float* in_bias,
                           float* state, long long state_stride, const int* token_item, const int* q_start, const int* q_len,
                           const int* seq_slot, int T, int items, int C, int taps, int silu, cudaStream_t stream) {
   MI_REQUIRE(T >= 0 && items >= 0 && C > 0 && taps >= 1 && taps <= MAX_TAPS, "causal_conv: bad sizes C=%d taps=%d (taps up to %d)", C, taps, MAX_TAPS);
@@ -575,14 +578,14 @@ MI_API int mi_causal_conv(void* out, int ldo, const void* x, int ldx, int dtype,
   if (T == 0) return 0;
   dim3 grid((C + 255) / 256, T), sgrid((C + 255) / 256, items);
   if (dtype == MI_BF16) {
-    mi::launch(causal_conv_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)x, ldx, w, bias,
+    mi::launch(causal_conv_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)x, ldx, w, bias, in_bias,
                (const float*)state, state_stride, token_item, q_start, seq_slot, C, taps, silu);
-    if (taps > 1) mi::launch(conv_state_kernel<__nv_bfloat16>, sgrid, dim3(256), 0, stream, state, state_stride, (const __nv_bfloat16*)x, ldx,
+    if (taps > 1) mi::launch(conv_state_kernel<__nv_bfloat16>, sgrid, dim3(256), 0, stream, state, state_stride, (const __nv_bfloat16*)x, ldx, in_bias,
                              q_start, q_len, seq_slot, C, taps);
   } else if (dtype == MI_F32) {
-    mi::launch(causal_conv_kernel<float>, grid, dim3(256), 0, stream, (float*)out, ldo, (const float*)x, ldx, w, bias,
+    mi::launch(causal_conv_kernel<float>, grid, dim3(256), 0, stream, (float*)out, ldo, (const float*)x, ldx, w, bias, in_bias,
                (const float*)state, state_stride, token_item, q_start, seq_slot, C, taps, silu);
-    if (taps > 1) mi::launch(conv_state_kernel<float>, sgrid, dim3(256), 0, stream, state, state_stride, (const float*)x, ldx,
+    if (taps > 1) mi::launch(conv_state_kernel<float>, sgrid, dim3(256), 0, stream, state, state_stride, (const float*)x, ldx, in_bias,
                              q_start, q_len, seq_slot, C, taps);
   } else {
     return mi_fail("causal_conv: unknown dtype %d", dtype);

@@ -519,22 +519,25 @@ def linear_batched(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, bias: Op
 
 
 def causal_conv(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
-                ctx, silu: bool = True) -> None:
+                ctx, silu: bool = True, in_bias: Optional[torch.Tensor] = None) -> None:
   """Short causal convolution over time per channel with the activation behind it, continuing from and updating the
   per-request state: ``out[t, c] = act(bias[c] + sum_k weight[c, taps - 1 - k] * x[t - k, c])``.  ``x`` and ``out`` may be
   column ranges of wider rows; ``state [slots, >= (taps - 1) * channels]`` float32 holds each request's last taps - 1
-  inputs (oldest first) and is brought up to date after the convolution (two launches)."""
+  inputs (oldest first) and is brought up to date after the convolution (two launches).  ``in_bias [channels]`` float32 is added
+  to every input ``x[t, c]`` (the bias of the projection that made ``x``; what lies before a request's start stays zero)
+  and the state keeps the inputs with it."""
   lib = common_lib()
   T, C = x.shape
   taps = weight.shape[1]
-  if weight.shape != (C, taps) or out.shape != (T, C) or out.dtype != x.dtype or (bias is not None and bias.shape != (C,)):
+  if (weight.shape != (C, taps) or out.shape != (T, C) or out.dtype != x.dtype or (bias is not None and bias.shape != (C,))
+      or (in_bias is not None and in_bias.shape != (C,))):
     raise KernelError("causal_conv: shapes do not match")
   if state.dim() != 2 or state.stride(1) != 1 or state.dtype != torch.float32:
     raise KernelError("causal_conv: the state must be float32 rows, one per request slot")
   xp, ldx = _cols(x, "causal_conv")
   op, ldo = _cols(out, "causal_conv")
   _check(lib, lib.mi_causal_conv(op, ldo, xp, ldx, _dt(x), _ptr(weight, torch.float32), _ptr(bias, torch.float32) if bias is not None else _ptr(None),
-                                 ctypes.c_void_p(state.data_ptr()), ctypes.c_longlong(state.stride(0)), _ptr(ctx.token_item, torch.int32),
+                                 _ptr(in_bias, torch.float32) if in_bias is not None else _ptr(None), ctypes.c_void_p(state.data_ptr()), ctypes.c_longlong(state.stride(0)), _ptr(ctx.token_item, torch.int32),
                                  _ptr(ctx.q_start, torch.int32), _ptr(ctx.q_len, torch.int32), _ptr(ctx.seq_slot, torch.int32),
                                  T, ctx.num_items, C, taps, int(bool(silu)), _stream()), kernels=2 if taps > 1 else 1)
 
@@ -690,6 +693,104 @@ def linear_attention(out: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: tor
     _ptr(segments, torch.float32) if segments is not None else none, _stream()), kernels=launches)
 
 
+def token_shift(out: torch.Tensor, resid: torch.Tensor, shift: Optional[torch.Tensor], state: Optional[torch.Tensor], ctx) -> None:
+  """out[t] = x[t] + (x[t - 1] - x[t]) * shift for the float32 rows ``x = resid``, written in ``out``'s dtype; ``x[t - 1]`` of an
+  item's first new token is the item's row of ``state [slots, >= width]`` float32 (zeros for a request's first token), which is
+  only read here.  Without ``shift``: a copy of the rows into ``out``'s dtype."""
+  lib = common_lib()
+  T, W = resid.shape
+  if out.shape != (T, W) or resid.dtype != torch.float32 or not (resid.is_contiguous() and out.is_contiguous()):
+    raise KernelError("token_shift: shapes do not match or rows are not contiguous")
+  if shift is not None and (shift.shape != (W,) or state is None or state.dim() != 2 or state.stride(1) != 1 or state.dtype != torch.float32
+                            or state.shape[1] < W):
+    raise KernelError("token_shift: the shift is one float32 per channel and needs float32 state rows of the width")
+  _check(lib, lib.mi_token_shift(_ptr(out), _dt(out), _ptr(resid, torch.float32), T, W,
+                                 _ptr(shift, torch.float32) if shift is not None else _ptr(None),
+                                 ctypes.c_void_p(state.data_ptr()) if shift is not None else _ptr(None),
+                                 ctypes.c_longlong(state.stride(0) if shift is not None else 0), _ptr(ctx.token_item, torch.int32),
+                                 _ptr(ctx.q_start, torch.int32), _ptr(ctx.seq_slot, torch.int32), _stream()))
+
+
+def norm_scaled_add(resid: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, mult: float, ctx,
+                    copy: Optional[torch.Tensor] = None, keep: Optional[torch.Tensor] = None) -> None:
+  """resid[t] += mult * weight * y[t] / sqrt(mean(y[t]^2) + eps) in float32, in place: the RMS norm of a sublayer's output
+  added to the residual rows.  ``copy [T, W]`` (``y``'s dtype) receives the new rows; ``keep [slots, >= W]`` float32 receives,
+  for the last new token of every item, the row as it was BEFORE the addition (the state of a token shift)."""
+  lib = common_lib()
+  T, W = resid.shape
+  if y.shape != (T, W) or weight.shape != (W,) or resid.dtype != torch.float32 or not (resid.is_contiguous() and y.is_contiguous()):
+    raise KernelError("norm_scaled_add: shapes do not match or rows are not contiguous")
+  if copy is not None and (copy.shape != (T, W) or copy.dtype != y.dtype or not copy.is_contiguous()):
+    raise KernelError("norm_scaled_add: the copy has the rows' shape and the sublayer output's dtype")
+  if keep is not None and (keep.dim() != 2 or keep.stride(1) != 1 or keep.dtype != torch.float32 or keep.shape[1] < W):
+    raise KernelError("norm_scaled_add: the kept rows are float32 state rows of the width")
+  _check(lib, lib.mi_norm_scaled_add(_ptr(resid, torch.float32), _ptr(y), _dt(y), _ptr(weight, torch.float32), T, W, ctypes.c_float(eps),
+                                     ctypes.c_float(mult), _ptr(copy) if copy is not None else _ptr(None), _dt(y),
+                                     ctypes.c_void_p(keep.data_ptr()) if keep is not None else _ptr(None),
+                                     ctypes.c_longlong(keep.stride(0) if keep is not None else 0), _ptr(ctx.token_item, torch.int32),
+                                     _ptr(ctx.q_start, torch.int32), _ptr(ctx.q_len, torch.int32), _ptr(ctx.seq_slot, torch.int32), _stream()))
+
+
+RECURRENCE_SEGMENTED_MIN_TOKENS = 512   # new tokens a request, on average, from which a bfloat16 diagonal recurrence runs in stretches side by side
+RECURRENCE_SEGMENT_MIN = 16             # ... the items of at least this many tokens a stretch
+
+
+def _recurrence_segmented(dtype: torch.dtype, ctx) -> int:
+  """Whether a step's diagonal recurrences take the form with stretches side by side: bfloat16 steps of long portions.  The
+  choice depends on the step's counts of tokens and items only, which are part of a recorded graph's identity."""
+  return int(dtype == torch.bfloat16 and ctx.num_tokens >= RECURRENCE_SEGMENTED_MIN_TOKENS * max(1, ctx.num_items)
+             and os.environ.get("MINIINFER_B200_RECURRENCE_SEGMENTS", "1") != "0")
+
+
+def _state_rows_arg(state: torch.Tensor, width: int, what: str):
+  if state.dim() != 2 or state.stride(1) != 1 or state.dtype != torch.float32 or state.shape[1] < width:
+    raise KernelError(f"{what}: the state must be float32 rows of at least {width} values, one per request slot")
+  return ctypes.c_void_p(state.data_ptr()), ctypes.c_longlong(state.stride(0))
+
+
+def rglru_recurrence(out: torch.Tensor, u: torch.Tensor, gates: torch.Tensor, y: torch.Tensor, r_bias: torch.Tensor, i_bias: torch.Tensor,
+                     y_bias: Optional[torch.Tensor], lam: torch.Tensor, state: torch.Tensor, ctx, blocks: int) -> None:
+  """The real-gated linear recurrent unit over the channels of ``u [T, C]``: with ``gates [T, blocks, 2 C / blocks]`` float32 (a
+  block's logits of r, then of i), ``r = sigmoid(. + r_bias)``, ``i = sigmoid(. + i_bias)``, ``a = exp(-8 r softplus(lam))``,
+  ``S <- a S + sqrt(1 - a^2) i u`` from the item's row of ``state``, and ``out = S * gelu_tanh(y + y_bias)``.  ``u``, ``y``, ``out``
+  may be column ranges of wider rows; biases and ``lam`` are float32 ``[C]``."""
+  lib = common_lib()
+  T, C = u.shape
+  if (out.shape != (T, C) or y.shape != (T, C) or gates.shape != (T, 2 * C) or gates.dtype != torch.float32 or not gates.is_contiguous()
+      or out.dtype != u.dtype or y.dtype != u.dtype or C % blocks):
+    raise KernelError("rglru_recurrence: shapes or dtypes do not match")
+  for b in (r_bias, i_bias, lam) + ((y_bias,) if y_bias is not None else ()):
+    if b.shape != (C,) or b.dtype != torch.float32:
+      raise KernelError("rglru_recurrence: biases and lam are one float32 per channel")
+  (op, ldo), (up, ldu), (yp, ldy) = _cols(out, "rglru_recurrence"), _cols(u, "rglru_recurrence"), _cols(y, "rglru_recurrence")
+  sp, ss = _state_rows_arg(state, C, "rglru_recurrence")
+  _check(lib, lib.mi_rglru_recurrence(op, ldo, up, ldu, _ptr(gates, torch.float32), 2 * C, yp, ldy, _dt(u), _ptr(r_bias, torch.float32),
+                                      _ptr(i_bias, torch.float32), _ptr(y_bias, torch.float32) if y_bias is not None else _ptr(None),
+                                      _ptr(lam, torch.float32), sp, ss, _ptr(ctx.q_start, torch.int32), _ptr(ctx.q_len, torch.int32),
+                                      _ptr(ctx.seq_slot, torch.int32), ctx.num_items, C, blocks, _recurrence_segmented(u.dtype, ctx),
+                                      RECURRENCE_SEGMENT_MIN, _stream()))
+
+
+def mingru_recurrence(out: torch.Tensor, proj: torch.Tensor, z_bias: Optional[torch.Tensor], x_bias: Optional[torch.Tensor],
+                      state: torch.Tensor, ctx) -> None:
+  """The minimal gated recurrence over ``proj [T, 3 C]`` (logits of z, then x, then g): ``z = sigmoid(. + z_bias)``, the candidate
+  ``c = x + 1/2`` where ``x = . + x_bias >= 0`` and ``sigmoid(x)`` below, ``S <- (1 - z) S + z c`` from the item's row of ``state``,
+  ``out = S * silu(g)``."""
+  lib = common_lib()
+  T, C = out.shape
+  if proj.shape != (T, 3 * C) or proj.dtype != out.dtype:
+    raise KernelError("mingru_recurrence: shapes or dtypes do not match")
+  for b in (z_bias, x_bias):
+    if b is not None and (b.shape != (C,) or b.dtype != torch.float32):
+      raise KernelError("mingru_recurrence: biases are one float32 per channel")
+  (op, ldo), (pp, ld) = _cols(out, "mingru_recurrence"), _cols(proj, "mingru_recurrence")
+  sp, ss = _state_rows_arg(state, C, "mingru_recurrence")
+  _check(lib, lib.mi_mingru_recurrence(op, ldo, pp, ld, _dt(out), _ptr(z_bias, torch.float32) if z_bias is not None else _ptr(None),
+                                       _ptr(x_bias, torch.float32) if x_bias is not None else _ptr(None), sp, ss,
+                                       _ptr(ctx.q_start, torch.int32), _ptr(ctx.q_len, torch.int32), _ptr(ctx.seq_slot, torch.int32),
+                                       ctx.num_items, C, _recurrence_segmented(out.dtype, ctx), RECURRENCE_SEGMENT_MIN, _stream()))
+
+
 def hyper_connection(res: torch.Tensor, streams: torch.Tensor, y: Optional[torch.Tensor], mix: Optional[torch.Tensor],
                      out_w: Optional[torch.Tensor], in_w: Optional[torch.Tensor], norm_weight: Optional[torch.Tensor], eps: float,
                      rows: Optional[torch.Tensor] = None, write_back: bool = True) -> None:
@@ -815,20 +916,43 @@ def moe_rows(num_pairs: int, num_experts: int, tile: int) -> int:
   return -(-(num_pairs + num_experts * (tile - 1)) // tile) * tile
 
 
-def routed_experts(out: torch.Tensor, x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, gate_up: torch.Tensor,
-                   down: torch.Tensor, top: int, workspace) -> None:
+GLU_KINDS = {"silu": 0, "clamped": 1}      # the gated activations of common.cuh (MiGlu)
+
+
+def _glu(kind: str, limit: float):
+  if kind not in GLU_KINDS or (kind == "clamped" and not limit > 0):
+    raise KernelError(f"gated activation {kind!r} is not known ({', '.join(GLU_KINDS)}) or its limit {limit!r} is not positive")
+  return GLU_KINDS[kind], ctypes.c_float(float(limit))
+
+
+def routed_experts(out: torch.Tensor, x: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], gate_up: torch.Tensor,
+                   down: torch.Tensor, top: int, workspace, weights: str = "sigmoid_share", glu: str = "silu", limit: float = 0.0,
+                   shared: Optional[torch.Tensor] = None, shared_gated: bool = False) -> None:
   """out[t] = sum over the ``top`` chosen experts of weight * down_e(silu(gate_e x) * up_e x).
 
   ``router [E, H]`` in the rows' dtype and ``correction [E]`` float32: logits ``router x`` accumulated in float32 (bfloat16
   operands multiply exactly in float32), scores their sigmoid; the ``top`` experts of largest
   score + correction are chosen; weights are their scores divided by the scores' sum (+ 1e-20).  ``gate_up [E, 2 ff, H]``
   (an expert's gate rows, then its up rows) and ``down [E, H, ff]`` in the rows' dtype.  Six or seven launches, nothing read
-  back by the host; scratch from ``workspace``."""
+  back by the host; scratch from ``workspace``.
+
+  ``weights="softmax_chosen"``: the ``top`` largest logits are chosen (``correction`` may be None) and the weights are the
+  softmax over the chosen logits alone.  ``glu``/``limit``: the experts' gated activation (``silu``, or ``clamped`` with its
+  limit: ``g' = min(g, L)``, ``u' = clamp(u, -L, L)``, ``g' sigmoid(1.702 g') (u' + 1)``).  ``shared [T, H]``: the output of an
+  expert that every token runs through, added to the sum; with ``shared_gated`` the router has one row more than there are
+  experts, and the shared rows are multiplied with the sigmoid of that row's logit, one number a token."""
   lib = common_lib()
   T, H = x.shape
-  E = router.shape[0]
+  E = router.shape[0] - (1 if shared_gated else 0)
   ff = down.shape[2]
-  if router.shape != (E, H) or correction.shape != (E,) or gate_up.shape != (E, 2 * ff, H) or down.shape != (E, H, ff) or out.shape != (T, H):
+  if weights not in ("sigmoid_share", "softmax_chosen") or (correction is None and weights == "sigmoid_share"):
+    raise KernelError(f"routed_experts: weights={weights!r} is not known, or sigmoid shares without their correction")
+  if shared_gated and shared is None:
+    raise KernelError("routed_experts: a gate for the shared expert without its rows")
+  if shared is not None and (shared.shape != (T, H) or shared.dtype != out.dtype or not shared.is_contiguous()):
+    raise KernelError("routed_experts: the shared expert's rows do not match the output")
+  kind, lim = _glu(glu, limit)
+  if router.shape != (E + (1 if shared_gated else 0), H) or (correction is not None and correction.shape != (E,)) or gate_up.shape != (E, 2 * ff, H) or down.shape != (E, H, ff) or out.shape != (T, H):
     raise KernelError(f"routed_experts: shapes do not match: x {tuple(x.shape)}, router {tuple(router.shape)}, "
                       f"gate_up {tuple(gate_up.shape)}, down {tuple(down.shape)}")
   if gate_up.dtype != x.dtype or down.dtype != x.dtype or out.dtype != x.dtype or router.dtype != x.dtype:
@@ -852,9 +976,13 @@ def routed_experts(out: torch.Tensor, x: torch.Tensor, router: torch.Tensor, cor
   act = workspace.buffer("moe_act", (rows, ff), x.dtype)
   y = None if on_tc else workspace.buffer("moe_y", (rows, H), torch.float32)
   dt, st = _dt(x), _stream()
-  logits = workspace.buffer("moe_logits", (T, E), torch.float32)
+  Z = router.shape[0]
+  logits = workspace.buffer("moe_logits", (T, Z), torch.float32)
   linear(logits, x, router)
-  _check(lib, lib.mi_moe_route(_ptr(logits, torch.float32), T, _ptr(correction, torch.float32), E, top, _ptr(idx), _ptr(wts), st))
+  _check(lib, lib.mi_moe_route(_ptr(logits, torch.float32), Z, T, _ptr(correction, torch.float32) if correction is not None else _ptr(None), E, top,
+                               1 if weights == "softmax_chosen" else 0, _ptr(idx), _ptr(wts), st))
+  shared_args = (_ptr(shared) if shared is not None else _ptr(None),
+                 ctypes.c_void_p(logits.data_ptr() + 4 * E) if shared_gated else _ptr(None), Z)
   _check(lib, lib.mi_moe_align(_ptr(idx), pairs, E, tile, _ptr(sorted_pair), _ptr(pos_of), _ptr(tile_expert), rows, tiles, st))
   if on_tc:
     xs = workspace.buffer("moe_rows", (rows, H), x.dtype)
@@ -862,14 +990,15 @@ def routed_experts(out: torch.Tensor, x: torch.Tensor, router: torch.Tensor, cor
     status = workspace.zeros("gemm_tc_status", 1, torch.int32)
     _check(lib, lib.mi_moe_gather(_ptr(xs), _ptr(x), _ptr(sorted_pair), rows, top, H, st))
     _check(lib, lib.mi_gemm_tc_grouped_bf16(_ptr(act), _ptr(xs), _ptr(gate_up), rows, ff, H, ff, E, 1, _ptr(tile_expert), tile,
-                                            _ptr(status, torch.int32), _tc_pairs(), st))
+                                            _ptr(status, torch.int32), _tc_pairs(), kind, lim, st))
     _check(lib, lib.mi_gemm_tc_grouped_bf16(_ptr(y16), _ptr(act), _ptr(down), rows, H, ff, H, E, 0, _ptr(tile_expert), tile,
-                                            _ptr(status, torch.int32), _tc_pairs(), st))
-    _check(lib, lib.mi_moe_combine(_ptr(out), _dt(out), _ptr(y16), BF16, _ptr(pos_of), _ptr(wts), T, top, H, st))
+                                            _ptr(status, torch.int32), _tc_pairs(), 0, ctypes.c_float(0.0), st))
+    _check(lib, lib.mi_moe_combine(_ptr(out), _dt(out), _ptr(y16), BF16, _ptr(pos_of), _ptr(wts), T, top, H, *shared_args, st))
     return
-  _check(lib, lib.mi_moe_gemm(_ptr(x), dt, H, _ptr(gate_up), _ptr(act), _ptr(sorted_pair), _ptr(tile_expert), tiles, tile, ff, H, top, 1, st))
-  _check(lib, lib.mi_moe_gemm(_ptr(act), dt, ff, _ptr(down), _ptr(y), _ptr(sorted_pair), _ptr(tile_expert), tiles, tile, H, ff, top, 0, st))
-  _check(lib, lib.mi_moe_combine(_ptr(out), _dt(out), _ptr(y), F32, _ptr(pos_of), _ptr(wts), T, top, H, st))
+  _check(lib, lib.mi_moe_gemm(_ptr(x), dt, H, _ptr(gate_up), _ptr(act), _ptr(sorted_pair), _ptr(tile_expert), tiles, tile, ff, H, top, 1, kind, lim, st))
+  _check(lib, lib.mi_moe_gemm(_ptr(act), dt, ff, _ptr(down), _ptr(y), _ptr(sorted_pair), _ptr(tile_expert), tiles, tile, H, ff, top, 0, 0,
+                              ctypes.c_float(0.0), st))
+  _check(lib, lib.mi_moe_combine(_ptr(out), _dt(out), _ptr(y), F32, _ptr(pos_of), _ptr(wts), T, top, H, *shared_args, st))
 
 
 def linear_swiglu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace, force_skinny: bool = False,
@@ -929,6 +1058,42 @@ def linear_tc(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace) ->
   _check(lib, lib.mi_gemm_tc_bf16(_ptr(out), _ptr(x), _ptr(w), M, N, K, N, _ptr(status, torch.int32), _tc_pairs(), _stream()))
 
 
+def glu_mul(out: torch.Tensor, gate_up: torch.Tensor, glu: str = "silu", limit: float = 0.0) -> None:
+  """out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i] with the gated activation ``glu`` (see ``routed_experts``)."""
+  lib = common_lib()
+  T, I = out.shape
+  if gate_up.shape != (T, 2 * I) or gate_up.dtype != out.dtype:
+    raise KernelError("glu_mul: shapes or dtypes do not match")
+  kind, lim = _glu(glu, limit)
+  _check(lib, lib.mi_glu_mul(_ptr(out), _ptr(gate_up), _dt(out), T, I, kind, lim, _stream()))
+
+
+def linear_glu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace, glu: str = "silu", limit: float = 0.0) -> None:
+  """out[M, I] = act(x @ w[:I]^T) * (x @ w[I:]^T): the gate-and-up product of a gated feed-forward with the activation
+  ``glu``.  ``silu`` is ``linear_swiglu``; the others take the tcgen05 kernel with the activation in its epilogue from the
+  same number of rows on, and the product followed by the activation kernel below it."""
+  if glu == "silu":
+    linear_swiglu(out, x, w, workspace)
+    return
+  M, K = x.shape
+  I = out.shape[1]
+  if w.shape != (2 * I, K) or out.shape[0] != M or out.dtype != x.dtype:
+    raise KernelError(f"linear_glu: shapes do not match: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+  if M == 0:
+    return
+  kind, lim = _glu(glu, limit)
+  many = M >= (GEMM_TC_MIN_M if K >= 4096 else GEMM_TC_MIN_M_NARROW)
+  if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and many and K >= 64 and K % 8 == 0 and I % 8 == 0
+      and x.is_contiguous() and w.is_contiguous() and out.is_contiguous() and os.environ.get("MINIINFER_B200_GEMM_TC", "1") != "0"):
+    lib = common_lib()
+    status = workspace.zeros("gemm_tc_status", 1, torch.int32)
+    _check(lib, lib.mi_gemm_tc_glu_bf16(_ptr(out), _ptr(x), _ptr(w), M, I, K, I, _ptr(status, torch.int32), _tc_pairs(), kind, lim, _stream()))
+    return
+  gu = workspace.buffer("gate_up", (M, 2 * I), x.dtype)
+  linear(gu, x, w)
+  glu_mul(out, gu, glu, limit)
+
+
 def silu_mul(out: torch.Tensor, gate_up: torch.Tensor) -> None:
   lib = common_lib()
   T, I = out.shape
@@ -986,7 +1151,7 @@ def attention(out: torch.Tensor, qkv: torch.Tensor, kv_layer: torch.Tensor, bloc
               batch: AttentionBatch, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
               window: Optional[int], force_generic: bool = False, sink: Optional[torch.Tensor] = None,
               gate: Optional[torch.Tensor] = None, gate_offset: int = 0, out_hd: Optional[int] = None,
-              keep_first: int = 0) -> None:
+              keep_first: int = 0, softcap: float = 0.0, score_bias: Optional[torch.Tensor] = None) -> None:
   """out[t, h*hd:(h+1)*hd] = softmax(scale * q . K^T over the keys the token may see) V, reading
   K and V through the block table.  ``qkv`` holds the step's fused rows; q is its first part.
 
@@ -994,7 +1159,9 @@ def attention(out: torch.Tensor, qkv: torch.Tensor, kv_layer: torch.Tensor, bloc
   once, unscaled, with no key and no value; ``gate`` - rows ``[tokens, width]`` whose columns from ``gate_offset`` on hold,
   head after head, a gate for every output value: the output is multiplied with its sigmoid; ``out_hd`` - only the first
   ``out_hd`` values of each head are written, ``out`` being ``[tokens, heads * out_hd]`` (cache rows padded to ``head_dim``);
-  ``keep_first`` - with a window, every token also sees the first ``keep_first`` keys of its request."""
+  ``keep_first`` - with a window, every token also sees the first ``keep_first`` keys of its request; ``softcap`` > 0 - a
+  scaled score ``s`` becomes ``softcap * tanh(s / softcap)``; ``score_bias [heads]`` float32 - no softmax: the weight of a
+  visible key is ``sigmoid(s + score_bias[head])``, not normalised over the keys (no sink then)."""
   T = qkv.shape[0]
   ohd = head_dim if out_hd is None else int(out_hd)
   if out.shape != (T, num_heads * ohd) or out.dtype != qkv.dtype or kv_layer.dtype != qkv.dtype or not (0 < ohd <= head_dim):
@@ -1009,11 +1176,16 @@ def attention(out: torch.Tensor, qkv: torch.Tensor, kv_layer: torch.Tensor, bloc
     gate_stride = gate.shape[1]
     if gate.dtype != qkv.dtype or gate.shape[0] != T or gate_offset + num_heads * ohd > gate_stride or not gate.is_contiguous():
       raise KernelError("attention: the gate rows do not match")
+  if score_bias is not None and (score_bias.shape != (num_heads,) or score_bias.dtype != torch.float32 or sink is not None):
+    raise KernelError("attention: the score biases must be one float32 per query head, and go without sinks")
+  if softcap < 0:
+    raise KernelError(f"attention: softcap={softcap} must not be negative")
   opts = _AttentionOptions(sink, gate, gate_offset, gate_stride, ohd)
+  opts.softcap, opts.score_bias = float(softcap), score_bias
   win = int(window) if window else 0
   opts.keep_first = int(keep_first) if win else 0
   even = ohd % 2 == 0 and gate_offset % 2 == 0 and gate_stride % 2 == 0
-  if qkv.dtype == torch.bfloat16 and not force_generic and head_dim % 16 == 0 and 16 <= head_dim <= 256 and even:
+  if qkv.dtype == torch.bfloat16 and not force_generic and head_dim % 16 == 0 and 16 <= head_dim <= 256 and even and not opts.shaped_scores():
     _attention_bf16(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, head_dim, scale, win, page_size, opts)
     return
   lib = common_lib()
@@ -1021,17 +1193,25 @@ def attention(out: torch.Tensor, qkv: torch.Tensor, kv_layer: torch.Tensor, bloc
     _ptr(out), _ptr(qkv), qkv.shape[1], _dt(qkv), _ptr(kv_layer), _ptr(block_table, torch.int32),
     block_table.shape[1], _ptr(batch.token_item, torch.int32), _ptr(batch.positions, torch.int32),
     _ptr(batch.seq_slot, torch.int32), T, num_heads, num_kv_heads, head_dim, page_size,
-    ctypes.c_float(scale), win, opts.sink_ptr(), opts.gate_ptr(), gate_stride, ohd, opts.keep_first, _stream()))
+    ctypes.c_float(scale), win, opts.sink_ptr(), opts.gate_ptr(), gate_stride, ohd, opts.keep_first, ctypes.c_float(opts.softcap),
+    opts.score_bias_ptr(), _stream()))
 
 
 class _AttentionOptions:
   """The optional sink, output gate and output width of an attention call, as the kernels take them."""
 
-  __slots__ = ("sink", "gate", "gate_offset", "gate_stride", "out_hd", "keep_first")
+  __slots__ = ("sink", "gate", "gate_offset", "gate_stride", "out_hd", "keep_first", "softcap", "score_bias")
 
   def __init__(self, sink, gate, gate_offset, gate_stride, out_hd, keep_first=0):
     self.sink, self.gate, self.gate_offset, self.gate_stride, self.out_hd = sink, gate, gate_offset, gate_stride, out_hd
     self.keep_first = keep_first
+    self.softcap, self.score_bias = 0.0, None
+
+  def shaped_scores(self) -> bool:
+    return self.softcap > 0 or self.score_bias is not None
+
+  def score_bias_ptr(self):
+    return _ptr(self.score_bias, torch.float32) if self.score_bias is not None else _ptr(None)
 
   def plain(self, head_dim: int) -> bool:
     return self.sink is None and self.gate is None and self.out_hd == head_dim

@@ -76,6 +76,5 @@ class ModelSpec:
     """The cache need of every run-list entry (None: it keeps nothing of its own)."""
     specs: List[Optional[CacheSpec]] = []
     for run in self.run_list:
-      mixer = self.blocks[run.block].mixer_part()
-      specs.append(None if (run.cache_of is not None or mixer is None) else mixer.cache_spec())
+      specs.append(None if run.cache_of is not None else self.blocks[run.block].cache_spec())
     return specs

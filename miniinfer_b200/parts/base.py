@@ -37,11 +37,18 @@ from ..cache.specs import CacheSpec
 
 @dataclass(frozen=True)
 class Piece:
-  """A tensor of the weights file that fills rows ``row_start .. row_start + shape[0]`` of a parameter."""
+  """A tensor of the weights file that fills rows ``row_start .. row_start + shape[0]`` of a parameter.  With ``of`` > 0 the
+  file tensor is a stack ``[of, *shape]`` (the square matrices of a block-diagonal map, say) and the piece is its entry
+  ``part``."""
 
   file_name: str
   row_start: int
   shape: Tuple[int, ...]
+  part: int = 0
+  of: int = 0
+
+  def file_shape(self) -> Tuple[int, ...]:
+    return ((self.of,) if self.of else ()) + tuple(self.shape)
 
 
 @dataclass
@@ -229,6 +236,11 @@ class Head(Part):
 class Block(Part):
   def mixer_part(self) -> Optional[Mixer]:
     return None
+
+  def cache_spec(self) -> Optional[CacheSpec]:
+    """What a run of this block keeps for a request: its mixer's need, unless the block keeps something of its own."""
+    mixer = self.mixer_part()
+    return mixer.cache_spec() if mixer is not None else None
 
   def forward(self, resid: torch.Tensor, pending: Optional[torch.Tensor], ctx, cache) -> Optional[torch.Tensor]:
     raise NotImplementedError

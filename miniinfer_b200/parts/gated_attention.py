@@ -21,6 +21,9 @@ key/value head ``i // (H / G)``), query/key size ``dim`` and value size ``vdim``
     ``keep_first``, if ``j < keep_first`` and ``j <= i``: the first tokens stay visible, at their true positions;
   * ``softmax`` over ``scale * q . k`` whose denominator also holds ``exp(sink)`` of the query head (``sinks``), a term
     with no key and no value;
+  * ``softcap`` > 0: a scaled score ``s`` becomes ``softcap * tanh(s / softcap)`` before the weights are made;
+  * ``weights="sigmoid"``: no softmax - the weight of a visible key is ``sigmoid(s + b)`` with ``b`` a learned number per
+    query head (file tensor ``pb``), and the weights are not normalised over the keys (``sinks`` must be off);
   * the heads' outputs, side by side, are multiplied element by element with ``sigmoid(g)`` (``gated``), then projected.
 
 Every option can be switched off, so other designs may take the parts they need.  The cache keeps keys and values in
@@ -46,7 +49,7 @@ class GatedAttentionMixer(AttentionMixer):
                value_mix: Optional[str] = None, value_mix_key: str = "value_mix_source",
                tensors: Optional[Dict[str, str]] = None, rotary: Optional[PositionEncoding] = None,
                rotary_interleaved: bool = False, norm_weights: bool = False, values_from_keys: bool = False,
-               keep_first: int = 0, biases: bool = False, norm_over: str = "head"):
+               keep_first: int = 0, biases: bool = False, norm_over: str = "head", softcap: float = 0.0, weights: str = "softmax"):
     super().__init__(name, hidden_size, num_heads, num_kv_heads, dim, scale, norm_eps, rotary, window)
     if values_from_keys and (vdim != dim or value_mix is not None):
       raise ValueError(f"{name}: values that are the keys have the keys' size ({dim}, got vdim={vdim}) and are not mixed")
@@ -56,6 +59,12 @@ class GatedAttentionMixer(AttentionMixer):
       raise ValueError(f"{name}: norm_over must be 'head' or 'projection', got {norm_over!r}")
     if biases and (values_from_keys or value_mix is not None):
       raise ValueError(f"{name}: biases go with projected, unmixed values")
+    if weights not in ("softmax", "sigmoid") or (weights == "sigmoid" and sinks):
+      raise ValueError(f"{name}: weights must be 'softmax' or 'sigmoid' (got {weights!r}), and sigmoid weights take no sink")
+    if not softcap >= 0:
+      raise ValueError(f"{name}: softcap must not be negative, got {softcap!r}")
+    self.softcap = float(softcap)
+    self.sigmoid_weights = weights == "sigmoid"
     self.biases = bool(biases)
     self.norm_whole = norm_over == "projection"
     self.rotary_interleaved = bool(rotary_interleaved)
@@ -74,7 +83,7 @@ class GatedAttentionMixer(AttentionMixer):
     self.value_mix = value_mix
     self.value_mix_key = value_mix_key
     t = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "sink": "sink", "mix": "vmix", "q_norm": "q.norm", "k_norm": "k.norm",
-         "q_bias": "q.b", "k_bias": "k.b", "v_bias": "v.b"}
+         "q_bias": "q.b", "k_bias": "k.b", "v_bias": "v.b", "score_bias": "pb"}
     t.update(tensors or {})
     self.tensors = t
     H, G = num_heads, num_kv_heads
@@ -107,6 +116,8 @@ class GatedAttentionMixer(AttentionMixer):
         Piece(f"{n}.{t['v_bias']}", self.v_off, (G * Dv,))]], init="half_noise")
     if self.sinks:
       specs["sink"] = ParamSpec((H,), "vector", [whole(f"{n}.{t['sink']}", (H,))])
+    if self.sigmoid_weights:
+      specs["score_bias"] = ParamSpec((H,), "vector", [whole(f"{n}.{t['score_bias']}", (H,))])
     if self.value_mix is not None:
       # the layer whose values are the source carries the scalar too (unused), as its file does
       specs["mix"] = ParamSpec((), "vector", [whole(f"{n}.{t['mix']}", ())], init="half_noise")
@@ -154,7 +165,8 @@ class GatedAttentionMixer(AttentionMixer):
     attn = ctx.ws.buffer("attn_out", (T, H * Dv), ctx.dtype)
     ops.attention(attn, q_heads, cache.tensor, ctx.block_tables[cache.group], self._batch(ctx), H, G, hdp, self.scale,
                   self.window, sink=self.sink if self.sinks else None, gate=proj if self.gated else None,
-                  gate_offset=self.g_off, out_hd=Dv, keep_first=self.keep_first)
+                  gate_offset=self.g_off, out_hd=Dv, keep_first=self.keep_first, softcap=self.softcap,
+                  score_bias=self.score_bias if self.sigmoid_weights else None)
     out = ctx.ws.buffer(self.out_buffer, (T, self.hidden_size), ctx.dtype)
     ops.linear(out, attn, self.o)
     return out

@@ -32,13 +32,18 @@ def split_delta(delta: Delta) -> Tuple[Optional[torch.Tensor], Optional[torch.Te
 class RMSNorm(Norm):
   """``(offset + w) * x / sqrt(mean(x^2) + eps)`` in float32, the residual add (of one or two pending outputs) in front
   of it in the same kernel.  ``offset``: 0 for a weight stored as it is applied, 1 for a weight stored around zero (the
-  sum is made once, in float32, when the weights are bound).  ``weight_name``: the file tensor (default ``<name>.weight``)."""
+  sum is made once, in float32, when the weights are bound).  ``gain``: a constant the normed rows are multiplied with (a
+  model's logit scale on its final norm), folded into the applied weight the same way.  ``weight_name``: the file tensor
+  (default ``<name>.weight``).
 
-  def __init__(self, name: str, dim: int, eps: float, offset: float = 0.0, weight_name: Optional[str] = None):
+  ``add_scaled`` is the norm for blocks that norm a sublayer's OUTPUT: ``resid += mult * norm(y)``."""
+
+  def __init__(self, name: str, dim: int, eps: float, offset: float = 0.0, weight_name: Optional[str] = None, gain: float = 1.0):
     super().__init__(name)
     self.dim = dim
     self.eps = float(eps)
     self.offset = float(offset)
+    self.gain = float(gain)
     self.weight_name = weight_name or f"{name}.weight"
 
   def param_specs(self) -> Dict[str, ParamSpec]:
@@ -47,8 +52,19 @@ class RMSNorm(Norm):
 
   def bind(self, params) -> None:
     super().bind(params)
-    if self.offset != 0.0 and "weight" in params:
-      self.weight = params["weight"] + self.offset          # the stored tensor stays as the file has it
+    if (self.offset != 0.0 or self.gain != 1.0) and "weight" in params:
+      self.weight = (params["weight"] + self.offset) * self.gain          # the stored tensor stays as the file has it
+
+  def add_scaled(self, resid: torch.Tensor, y: torch.Tensor, mult: float, ctx, copy: bool = False,
+                 keep: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """``resid += mult * norm(y)`` in float32, in place.  ``copy``: the new rows are also returned in the compute dtype (the
+    residual rows themselves when that is float32).  ``keep``: per-request state rows that receive, for the last new token of
+    every item, the residual row as it was before the addition."""
+    out = None
+    if copy:
+      out = resid if ctx.dtype == torch.float32 else ctx.ws.buffer("resid_rows", (resid.shape[0], self.dim), ctx.dtype)
+    ops.norm_scaled_add(resid, y, self.weight, self.eps, mult, ctx, copy=out if out is not resid else None, keep=keep)
+    return out
 
   def as_rms(self):
     return self.weight, self.eps

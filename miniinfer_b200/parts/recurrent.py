@@ -178,3 +178,127 @@ class GatedDeltaMixer(Mixer):
     out = ctx.ws.buffer(self.out_buffer, (T, self.hidden_size), ctx.dtype)
     ops.linear(out, heads, self.w_o)
     return out
+
+
+class RglruMixer(Mixer):
+  """A recurrent block around a real-gated linear recurrent unit.  Two branches of ``channels`` values:
+
+    ``y = gelu_tanh(W_y h + b_y)``;   ``u = conv(W_x h + b_x) + conv_bias`` (causal, per channel, ``taps`` taps, no activation);
+    u in ``blocks`` equal parts, in each part ``b``:  ``r = sigmoid(Ra[b] u_b + ra_bias[b])``,  ``i = sigmoid(Ri[b] u_b + ri_bias[b])``;
+    ``log a = -rate * r * softplus(lam)``,  ``S <- a S + sqrt(1 - a^2) * i * u``  per channel, from zero;   out = ``W_o (S * y)``.
+
+  ``rate`` is the design's constant 8.  Gates, decays and the state are float32.  What the mixer keeps for a request: the
+  convolution's last ``taps - 1`` inputs (with their bias), then ``S``.  One fused product gives both branches; the two gate
+  matrices of a part are stacked, so one batched product gives both logits.  File tensors (after ``<name>.``): ``y``, ``y.b``,
+  ``x``, ``x.b``, ``conv``, ``conv.b``, ``ra``, ``ra.b``, ``ri``, ``ri.b``, ``lam``, ``o``."""
+
+  def __init__(self, name: str, hidden_size: int, channels: int, blocks: int, taps: int, tensors: Optional[Dict[str, str]] = None):
+    super().__init__(name)
+    if channels <= 0 or blocks <= 0 or taps <= 0 or channels % blocks:
+      raise ValueError(f"{name}: {channels} channels must split into {blocks} equal parts, and the convolution needs taps (got {taps})")
+    self.hidden_size, self.channels, self.blocks, self.taps = hidden_size, channels, blocks, taps
+    self.part = channels // blocks
+    t = {"y": "y", "y_b": "y.b", "x": "x", "x_b": "x.b", "conv": "conv", "conv_b": "conv.b", "ra": "ra", "ra_b": "ra.b", "ri": "ri",
+         "ri_b": "ri.b", "lam": "lam", "o": "o"}
+    t.update(tensors or {})
+    self.tensors = t
+    self.conv_floats = (taps - 1) * channels
+
+  def cache_spec(self) -> Optional[CacheSpec]:
+    return FixedStateSpec((self.conv_floats + self.channels,), "float32")
+
+  def param_specs(self) -> Dict[str, ParamSpec]:
+    W, C, B, P, K, n, t = self.hidden_size, self.channels, self.blocks, self.part, self.taps, self.name, self.tensors
+    # rows b * 2P .. of the stacked gate matrix: part b's Ra, then its Ri
+    gates = [p for b in range(B) for p in (Piece(f"{n}.{t['ra']}", 2 * P * b, (P, P), part=b, of=B),
+                                           Piece(f"{n}.{t['ri']}", 2 * P * b + P, (P, P), part=b, of=B))]
+    return {
+      "w_in": ParamSpec((2 * C, W), "matrix", [[Piece(f"{n}.{t['x']}", 0, (C, W)), Piece(f"{n}.{t['y']}", C, (C, W))]]),
+      "x_b": ParamSpec((C,), "vector", [whole(f"{n}.{t['x_b']}", (C,))], init="half_noise"),
+      "y_b": ParamSpec((C,), "vector", [whole(f"{n}.{t['y_b']}", (C,))], init="half_noise"),
+      "conv": ParamSpec((C, K), "vector", [whole(f"{n}.{t['conv']}", (C, K))], init="half_noise"),
+      "conv_b": ParamSpec((C,), "vector", [whole(f"{n}.{t['conv_b']}", (C,))]),
+      "gates": ParamSpec((2 * C, P), "matrix", [gates], init="fan_in"),
+      "ra_b": ParamSpec((B, P), "vector", [whole(f"{n}.{t['ra_b']}", (B, P))]),
+      "ri_b": ParamSpec((B, P), "vector", [whole(f"{n}.{t['ri_b']}", (B, P))]),
+      "lam": ParamSpec((C,), "vector", [whole(f"{n}.{t['lam']}", (C,))]),
+      "w_o": ParamSpec((W, C), "matrix", [whole(f"{n}.{t['o']}", (W, C))]),
+    }
+
+  def bind(self, params) -> None:
+    super().bind(params)
+    for k in ("ra_b", "ri_b"):      # one bias a channel, the parts one after the other
+      if k in params:
+        setattr(self, k, params[k].reshape(-1))
+
+  def validate(self, dtype: torch.dtype) -> None:
+    if self.taps > 16:
+      raise ValueError(f"{self.name}: the convolution takes up to 16 taps, got {self.taps}")
+    if dtype == torch.bfloat16 and (self.hidden_size % 8 or self.channels % 8):
+      raise ValueError(f"{self.name}: width={self.hidden_size} and channels={self.channels} must be multiples of 8 in bfloat16 "
+                       f"(rows are read 16 bytes at a time)")
+
+  def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+    T = x.shape[0]
+    C, B, P = self.channels, self.blocks, self.part
+    state = _state_rows(cache, self.name)
+    proj = ctx.ws.buffer("rglru_proj", (T, 2 * C), ctx.dtype)
+    ops.linear(proj, x, self.w_in)
+    u = ctx.ws.buffer("rglru_u", (T, C), ctx.dtype)
+    ops.causal_conv(u, proj[:, :C], self.conv, self.conv_b, state[:, :max(self.conv_floats, 1)], ctx, silu=False, in_bias=self.x_b)
+    gates = ctx.ws.buffer("rglru_gates", (T, 2 * C), torch.float32)
+    ops.linear_batched(gates.view(T, B, 2 * P), u.view(T, B, P), self.gates.view(B, 2 * P, P))
+    s = ctx.ws.buffer("rglru_s", (T, C), ctx.dtype)
+    ops.rglru_recurrence(s, u, gates, proj[:, C:], self.ra_b, self.ri_b, self.y_b, self.lam, state[:, self.conv_floats:], ctx, B)
+    out = ctx.ws.buffer(self.out_buffer, (T, self.hidden_size), ctx.dtype)
+    ops.linear(out, s, self.w_o)
+    return out
+
+
+class MinGruMixer(Mixer):
+  """A gated recurrence whose gates read only the current token (minGRU), over ``channels`` channels:
+
+    ``z = sigmoid(W_z h + b_z)``;  ``x = W_x h + b_x``;  the candidate ``c = x + 1/2`` where ``x >= 0`` and ``sigmoid(x)`` below;
+    ``S <- (1 - z) S + z c``  per channel, from zero;   out = ``W_o (S * silu(W_g h))``.
+
+  The gate, the candidate and the state are float32; the state is all the mixer keeps for a request.  One fused product gives
+  z's logits, x and g.  File tensors (after ``<name>.``): ``z``, ``z.b``, ``x``, ``x.b``, ``g``, ``o``."""
+
+  def __init__(self, name: str, hidden_size: int, channels: int, tensors: Optional[Dict[str, str]] = None):
+    super().__init__(name)
+    if channels <= 0:
+      raise ValueError(f"{name}: channels must be positive, got {channels}")
+    self.hidden_size, self.channels = hidden_size, channels
+    t = {"z": "z", "z_b": "z.b", "x": "x", "x_b": "x.b", "g": "g", "o": "o"}
+    t.update(tensors or {})
+    self.tensors = t
+
+  def cache_spec(self) -> Optional[CacheSpec]:
+    return FixedStateSpec((self.channels,), "float32")
+
+  def param_specs(self) -> Dict[str, ParamSpec]:
+    W, C, n, t = self.hidden_size, self.channels, self.name, self.tensors
+    return {
+      "w_in": ParamSpec((3 * C, W), "matrix", [[Piece(f"{n}.{t['z']}", 0, (C, W)), Piece(f"{n}.{t['x']}", C, (C, W)),
+                                                Piece(f"{n}.{t['g']}", 2 * C, (C, W))]]),
+      "z_b": ParamSpec((C,), "vector", [whole(f"{n}.{t['z_b']}", (C,))], init="half_noise"),
+      "x_b": ParamSpec((C,), "vector", [whole(f"{n}.{t['x_b']}", (C,))], init="half_noise"),
+      "w_o": ParamSpec((W, C), "matrix", [whole(f"{n}.{t['o']}", (W, C))]),
+    }
+
+  def validate(self, dtype: torch.dtype) -> None:
+    if dtype == torch.bfloat16 and (self.hidden_size % 8 or self.channels % 8):
+      raise ValueError(f"{self.name}: width={self.hidden_size} and channels={self.channels} must be multiples of 8 in bfloat16 "
+                       f"(rows are read 16 bytes at a time)")
+
+  def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+    T = x.shape[0]
+    C = self.channels
+    state = _state_rows(cache, self.name)
+    proj = ctx.ws.buffer("mingru_proj", (T, 3 * C), ctx.dtype)
+    ops.linear(proj, x, self.w_in)
+    s = ctx.ws.buffer("mingru_s", (T, C), ctx.dtype)
+    ops.mingru_recurrence(s, proj, self.z_b, self.x_b, state, ctx)
+    out = ctx.ws.buffer(self.out_buffer, (T, self.hidden_size), ctx.dtype)
+    ops.linear(out, s, self.w_o)
+    return out

@@ -102,8 +102,8 @@ def load_weights(spec: ModelSpec, model_dir: str, compute_dtype: torch.dtype, de
           missing.append(n)
           continue
         used.add(n)
-        if index[n][1] != tuple(p.shape):
-          wrong.append(f"{n}: file has {list(index[n][1])}, the model needs {list(p.shape)}")
+        if index[n][1] != p.file_shape():
+          wrong.append(f"{n}: file has {list(index[n][1])}, the model needs {list(p.file_shape())}")
       plan.append((part, local, ps, chosen))
 
   other: List[str] = []
@@ -151,7 +151,7 @@ def load_weights(spec: ModelSpec, model_dir: str, compute_dtype: torch.dtype, de
         continue
       dst = param if len(pieces) == 1 and p.row_start == 0 and tuple(p.shape) == tuple(ps.shape) \
         else param[p.row_start:p.row_start + p.shape[0]]
-      dst.copy_(src)
+      dst.copy_(src[p.part] if p.of else src)
     by_part.setdefault(id(part), {})[local] = param
     parts_by_id[id(part)] = part
   if other:

@@ -50,8 +50,13 @@ def random_state_dict(spec: ModelSpec, seed: int, dtype: torch.dtype = torch.bfl
     for ps in part.param_specs().values():
       for piece in ps.sources[0]:
         t = _draw(piece.shape, ps.init, spec.init_std, gen)
-        out[piece.file_name] = t.to(dtype if ps.role in ("matrix", "table") else torch.float32).contiguous() \
-          if ps.role != "int" else t.to(torch.int32)
+        t = t.to(dtype if ps.role in ("matrix", "table") else torch.float32).contiguous() if ps.role != "int" else t.to(torch.int32)
+        if piece.of:      # an entry of a stacked file tensor
+          if piece.file_name not in out:
+            out[piece.file_name] = torch.zeros(piece.file_shape(), dtype=t.dtype)
+          out[piece.file_name][piece.part] = t
+        else:
+          out[piece.file_name] = t
   return out
 
 

@@ -166,29 +166,109 @@ def _rotate(t, table, positions, interleaved):
   return out
 
 
-def routed_experts(out, x, router, correction, gate_up, down, top, workspace):
+def _glu(g, u, glu, limit):
+  if glu == "clamped":
+    g, u = torch.clamp(g, max=limit), torch.clamp(u, -limit, limit)
+    return g * torch.sigmoid(1.702 * g) * (u + 1.0)
+  return g * torch.sigmoid(g) * u
+
+
+def routed_experts(out, x, router, correction, gate_up, down, top, workspace, weights="sigmoid_share", glu="silu", limit=0.0,
+                   shared=None, shared_gated=False):
   T, H = x.shape
-  E, ff = router.shape[0], down.shape[2]
+  E, ff = down.shape[0], down.shape[2]
   z = x.float() @ router.float().t()
-  s = torch.sigmoid(z)
-  idx = torch.topk(s + correction, top, dim=-1).indices
-  w = torch.gather(s, 1, idx)
-  w = w / (w.sum(-1, keepdim=True) + 1e-20)
+  if weights == "softmax_chosen":
+    idx = torch.topk(z[:, :E], top, dim=-1).indices
+    w = torch.softmax(torch.gather(z, 1, idx), dim=-1)
+  else:
+    s = torch.sigmoid(z[:, :E])
+    idx = torch.topk(s + correction, top, dim=-1).indices
+    w = torch.gather(s, 1, idx)
+    w = w / (w.sum(-1, keepdim=True) + 1e-20)
   res = torch.zeros((T, H), dtype=torch.float32, device=x.device)
   for e in range(E):
     g = x.float() @ gate_up[e, :ff].float().t()
     u = x.float() @ gate_up[e, ff:].float().t()
-    act = (g * torch.sigmoid(g) * u).to(x.dtype).float()
+    act = _glu(g, u, glu, limit).to(x.dtype).float()
     y = act @ down[e].float().t()
     res += (w * (idx == e)).sum(-1, keepdim=True) * y
+  if shared is not None:
+    res += shared.float() * (torch.sigmoid(z[:, E:E + 1]) if shared_gated else 1.0)
   out.copy_(res.to(out.dtype))
 
 
+def glu_mul(out, gate_up, glu="silu", limit=0.0):
+  I = out.shape[1]
+  out.copy_(_glu(gate_up[:, :I].float(), gate_up[:, I:].float(), glu, limit).to(out.dtype))
+
+
+def linear_glu(out, x, w, workspace, glu="silu", limit=0.0):
+  gu = torch.empty((x.shape[0], w.shape[0]), dtype=x.dtype)
+  linear(gu, x, w)
+  glu_mul(out, gu, glu, limit)
+
+
+def token_shift(out, resid, shift, state, ctx):
+  if shift is None:
+    out.copy_(resid.to(out.dtype))
+    return
+  W = resid.shape[1]
+  for row0, n, slot in _items(ctx):
+    x = resid[row0:row0 + n]
+    before = torch.cat((state[slot, :W][None], x[:-1]), dim=0)
+    out[row0:row0 + n] = (x + (before - x) * shift).to(out.dtype)
+
+
+def norm_scaled_add(resid, y, weight, eps, mult, ctx, copy=None, keep=None):
+  W = resid.shape[1]
+  if keep is not None:
+    for row0, n, slot in _items(ctx):
+      keep[slot, :W] = resid[row0 + n - 1]
+  v = y.float()
+  resid += mult * weight * (v / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + eps))
+  if copy is not None:
+    copy.copy_(resid.to(copy.dtype))
+
+
+def rglru_recurrence(out, u, gates, y, r_bias, i_bias, y_bias, lam, state, ctx, blocks):
+  T, C = u.shape
+  P = C // blocks
+  g = gates.view(T, blocks, 2 * P)
+  r = torch.sigmoid(g[:, :, :P].reshape(T, C) + r_bias)
+  i = torch.sigmoid(g[:, :, P:].reshape(T, C) + i_bias)
+  log_a = -8.0 * r * torch.nn.functional.softplus(lam)
+  a = torch.exp(log_a)
+  b = torch.sqrt(-torch.expm1(2.0 * log_a)) * i * u.float()
+  yy = y.float() + (y_bias if y_bias is not None else 0.0)
+  gate = 0.5 * yy * (1.0 + torch.tanh(0.7978845608028654 * (yy + 0.044715 * yy ** 3)))
+  _diagonal(out, a, b, gate, state, ctx, C)
+
+
+def mingru_recurrence(out, proj, z_bias, x_bias, state, ctx):
+  C = out.shape[1]
+  zl = proj[:, :C].float() + (z_bias if z_bias is not None else 0.0)
+  x = proj[:, C:2 * C].float() + (x_bias if x_bias is not None else 0.0)
+  g = proj[:, 2 * C:].float()
+  z = torch.sigmoid(zl)
+  _diagonal(out, 1.0 - z, z * torch.where(x >= 0, x + 0.5, torch.sigmoid(x)), g * torch.sigmoid(g), state, ctx, C)
+
+
+def _diagonal(out, a, b, gate, state, ctx, C):
+  for row0, n, slot in _items(ctx):
+    S = state[slot, :C].clone()
+    for t in range(row0, row0 + n):
+      S = a[t] * S + b[t]
+      out[t] = (S * gate[t]).to(out.dtype)
+    state[slot, :C] = S
+
+
 def attention(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, head_dim, scale, window,
-              force_generic=False, sink=None, gate=None, gate_offset=0, out_hd=None, keep_first=0):
-  if sink is not None or gate is not None or (out_hd is not None and out_hd != head_dim) or keep_first:
+              force_generic=False, sink=None, gate=None, gate_offset=0, out_hd=None, keep_first=0, softcap=0.0, score_bias=None):
+  if sink is not None or gate is not None or (out_hd is not None and out_hd != head_dim) or keep_first or softcap or score_bias is not None:
     return _attention_with_options(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, head_dim, scale,
-                                   window, sink, gate, gate_offset, out_hd if out_hd is not None else head_dim, keep_first)
+                                   window, sink, gate, gate_offset, out_hd if out_hd is not None else head_dim, keep_first,
+                                   softcap, score_bias)
   T = qkv.shape[0]
   nh, nkv, hd = num_heads, num_kv_heads, head_dim
   P = kv_layer.shape[3]
@@ -214,7 +294,7 @@ def attention(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, h
 
 
 def _attention_with_options(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, window, sink, gate, gate_offset, ohd,
-                            keep_first=0):
+                            keep_first=0, softcap=0.0, score_bias=None):
   T = qkv.shape[0]
   P = kv_layer.shape[3]
   g = nh // nkv
@@ -231,6 +311,11 @@ def _attention_with_options(out, qkv, kv_layer, block_table, batch, nh, nkv, hd,
     k = kv_layer[pages, 0, :, js % P, :].float().repeat_interleave(g, dim=1)
     v = kv_layer[pages, 1, :, js % P, :].float().repeat_interleave(g, dim=1)
     s = torch.einsum("hd,nhd->hn", q[t], k) * scale
+    if softcap:
+      s = softcap * torch.tanh(s / softcap)
+    if score_bias is not None:
+      res[t] = torch.einsum("hn,nhd->hd", torch.sigmoid(s + score_bias[:, None]), v)[:, :ohd]
+      continue
     if sink is not None:
       s = torch.cat((s, sink.float()[:, None]), dim=1)
     pr = torch.softmax(s, dim=-1)[:, :js.numel()]
@@ -281,12 +366,12 @@ def _items(ctx):
   return list(zip(ctx.q_start.tolist(), ctx.q_len.tolist(), ctx.seq_slot.tolist()))
 
 
-def causal_conv(out, x, weight, bias, state, ctx, silu=True):
+def causal_conv(out, x, weight, bias, state, ctx, silu=True, in_bias=None):
   C, taps = weight.shape
   S = taps - 1
   for row0, n, slot in _items(ctx):
     old = state[slot, :S * C].view(S, C) if S else x.new_zeros((0, C), dtype=torch.float32)
-    seq = torch.cat((old.float(), x[row0:row0 + n].float()), dim=0)
+    seq = torch.cat((old.float(), x[row0:row0 + n].float() + (in_bias if in_bias is not None else 0.0)), dim=0)
     y = sum(seq[k:k + n] * weight[:, k] for k in range(taps))
     if bias is not None:
       y = y + bias
@@ -482,5 +567,6 @@ def install(monkeypatch) -> None:
   for name in ("embedding", "add_rmsnorm", "add_layernorm", "linear", "linear_swiglu", "qk_norm_rope_store", "qkv_norm_mix_store",
                "attention", "routed_experts", "silu_mul", "sample", "linear_normed", "linear_swiglu_normed", "linear_add",
                "add_rmsnorm_pair", "rms_pair_sum", "linear_batched", "causal_conv", "selective_scan", "gated_delta", "latent_down",
-               "latent_query", "linear_attention", "hyper_connection", "relu_squared", "linear_relu_squared", "scaled_pair_sum"):
+               "latent_query", "linear_attention", "hyper_connection", "relu_squared", "linear_relu_squared", "scaled_pair_sum",
+               "glu_mul", "linear_glu", "token_shift", "norm_scaled_add", "rglru_recurrence", "mingru_recurrence"):
     monkeypatch.setattr(ops, name, globals()[name])
