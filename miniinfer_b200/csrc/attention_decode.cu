@@ -25,7 +25,12 @@
 // (exp(sink), unscaled, no value); an output gate multiplies the output row with sigmoid(gate[token,
 // head, :]); out_hd < head size writes only the first out_hd values of a head (padded cache rows).
 //
+// Shaped scores (attention_scores.cuh): a cap on the scaled scores, and sigmoid weights that are not normalised over the
+// keys - a score enters the online softmax as the logarithm of its weight, the pieces merge as ever, and the merged
+// output is multiplied with 2^m where the softmax divides by the sum.
+//
 // Compiled once per head size: -DMI_HEAD_DIM=<multiple of 16, 16..256>.
+#include "attention_scores.cuh"
 #include "common.cuh"
 
 #ifndef MI_HEAD_DIM
@@ -90,6 +95,8 @@ struct DecodeArgs {
   const float* sink;             // [nh] or null
   const __nv_bfloat16* gate;     // [T, gate_stride], head h at h * out_hd; or null
   int gate_stride, out_hd;
+  float softcap;                 // shaped scores: the cap (0: none)
+  const float* score_bias;       // [nh]: sigmoid weights; null: softmax
 };
 
 // Gathers keys first .. first + BK of one kv head (K and V rows) into a stage; rows from `end` on are
@@ -172,6 +179,9 @@ decode_split_kernel(DecodeArgs a) {
       cp_async_commit();
     }
 
+    const bool shaped = a.softcap > 0.f || a.score_bias != nullptr, sigmoid = a.score_bias != nullptr;
+    const float row_bias[2] = {sigmoid && g < heads ? a.score_bias[kvh * G + g0 + g] : 0.f,
+                               sigmoid && g + 8 < heads ? a.score_bias[kvh * G + g0 + g + 8] : 0.f};
     uint32_t qf[KSTEPS][4];
     float o[NT_O][4];
 #pragma unroll
@@ -218,7 +228,8 @@ decode_split_kernel(DecodeArgs a) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int j = key0 + i * 8 + 2 * t + (c & 1);
-          const float v = j < k_end ? s[i][c] * scale2 : -INFINITY;
+          const float v = j < k_end ? (shaped ? mi::shaped_logit2(s[i][c], a.scale, a.softcap, sigmoid, row_bias[c >> 1]) : s[i][c] * scale2)
+                                    : -INFINITY;
           s[i][c] = v;
           mx[c >> 1] = fmaxf(mx[c >> 1], v);
         }
@@ -341,7 +352,7 @@ decode_split_kernel(DecodeArgs a) {
     }
     l = mi::warp_sum(l);
     if (a.sink) l += exp2f(sink2 - m);
-    const float inv = 1.f / l;
+    const float inv = a.score_bias ? exp2f(m) : 1.f / l;      // sigmoid weights: the sums hold weight * 2^(-m), nothing is divided
     float acc = 0.f;
     const int first = min(n_splits, 32);
     // sixteen loads in flight: with many query heads on a kv head a warp merges dozens of (head, 32 dims) in turn
@@ -384,7 +395,7 @@ decode_merge_kernel(DecodeArgs a) {
   float l = 0.f;
   for (int s = 0; s < n_splits; ++s) l = fmaf(ml[2 * s + 1], exp2f(ml[2 * s] - m), l);
   if (a.sink) l += exp2f(sink2 - m);
-  const float inv = 1.f / l;
+  const float inv = a.score_bias ? exp2f(m) : 1.f / l;
   for (int d = threadIdx.x; d < a.out_hd; d += blockDim.x) {
     float acc = 0.f;
 #pragma unroll 8
@@ -412,7 +423,9 @@ MI_API int mi_attention_decode_bf16(void* out, const void* q_base, int q_stride,
                                     const int* q_start, const int* ctx_len, const int* seq_slot, float* scratch,
                                     int* counters, int n_dec, int nh, int nkv, int page_size, float scale,
                                     int window, int chunk, int max_splits, const float* sink, const void* gate,
-                                    int gate_stride, int out_hd, int keep_first, cudaStream_t stream) {
+                                    int gate_stride, int out_hd, int keep_first, float softcap, const float* score_bias,
+                                    cudaStream_t stream) {
+  MI_REQUIRE(!(softcap < 0.f) && !(sink && score_bias), "attention_decode: softcap must not be negative, and sigmoid weights take no sink");
   MI_REQUIRE(out_hd > 0 && out_hd <= HD, "attention_decode: out_hd=%d must lie in 1..%d", out_hd, HD);
   MI_REQUIRE(keep_first >= 0, "attention_decode: keep_first=%d must not be negative", keep_first);
   MI_REQUIRE(n_dec >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_decode: bad head counts nh=%d nkv=%d", nh, nkv);
@@ -439,6 +452,7 @@ MI_API int mi_attention_decode_bf16(void* out, const void* q_base, int q_stride,
   a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window; a.chunk = chunk; a.max_splits = max_splits; a.keep_first = keep_first;
   a.scale = scale;
   a.sink = sink; a.gate = (const __nv_bfloat16*)gate; a.gate_stride = gate_stride; a.out_hd = out_hd;
+  a.softcap = softcap; a.score_bias = score_bias;
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);

@@ -6,6 +6,7 @@
 
 #include <cuda.h>
 
+#include "attention_scores.cuh"
 #include "common.cuh"
 
 namespace {
@@ -87,10 +88,18 @@ __device__ __forceinline__ uint32_t tile_addr(uint32_t tile, int r, int c) {
 // the tile's keys and values in shared memory as the tensor copies write them (128-byte swizzle);
 // `jb`: the token of the tile's first row; qf: the query fragments (head lane / 4, dims 16k + 2(lane % 4) ..
 // and + 8); o[db][c]: dim db*16 + lane/4 + 8*(c/2), head 2(lane % 4) + (c & 1); m_run, l_run: heads
-// 2(lane % 4) and + 1, the sums still spread over the lanes that hold different keys.
+// 2(lane % 4) and + 1, the sums still spread over the lanes that hold different keys.  `shape`: shaped scores
+// (attention_scores.cuh), with the biases of this thread's two heads.
+struct TileScores {
+  bool shaped, sigmoid;
+  float scale, softcap;
+  float bias[2];
+};
+__device__ __forceinline__ TileScores plain_scores() { return TileScores{false, false, 0.f, 0.f, {0.f, 0.f}}; }
+
 __device__ __forceinline__ void consume_tile(uint32_t kt, uint32_t vt, const uint32_t (&qf)[KSTEPS][2], float (&o)[HD / 16][4],
                                              float (&m_run)[2], float (&l_run)[2], int jb, int k_lo, int k_end, float scale2,
-                                             int lane) {
+                                             int lane, const TileScores& shape = plain_scores()) {
   const int g = lane >> 2;
   const int lm = lane >> 3, lr = lane & 7;
   // S^T = K Q^T: 64 keys x 8 heads; sc[mb][c]: key mb*16 + g + 8*(c/2), head 2t + (c&1)
@@ -116,7 +125,9 @@ __device__ __forceinline__ void consume_tile(uint32_t kt, uint32_t vt, const uin
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       const int j = jb + i * 16 + g + 8 * (c >> 1);
-      const float v = (j >= k_lo && j < k_end) ? sc[i][c] * scale2 : -INFINITY;
+      const float v = (j >= k_lo && j < k_end)
+                          ? (shape.shaped ? mi::shaped_logit2(sc[i][c], shape.scale, shape.softcap, shape.sigmoid, shape.bias[c & 1]) : sc[i][c] * scale2)
+                          : -INFINITY;
       sc[i][c] = v;
       mx[c & 1] = fmaxf(mx[c & 1], v);
     }

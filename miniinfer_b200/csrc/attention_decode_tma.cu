@@ -95,6 +95,8 @@ struct Args {
   const float* sink;             // [nh] or null: a logit per query head whose exponential joins the denominator once
   const __nv_bfloat16* gate;     // [T, gate_stride] or null: the output is multiplied with sigmoid(gate[row, head * HD + d])
   int gate_stride;
+  float softcap;                 // shaped scores (attention_scores.cuh): the cap (0: none)
+  const float* score_bias;       // [nh]: sigmoid weights, nothing normalised over the keys; null: softmax
 };
 
 __device__ __forceinline__ float gated(const Args& a, float y, int row, int head, int d) {
@@ -337,7 +339,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
             for (int sp = lane; sp < ns; sp += 32) l = fmaf(merge_s[2 * (gh * ns + sp) + 1], exp2f(merge_s[2 * (gh * ns + sp)] - m), l);
             l = mi::warp_sum(l);
             if (a.sink) l += exp2f(sink2 - m);
-            const float inv = 1.f / l;
+            const float inv = a.score_bias ? exp2f(m) : 1.f / l;      // sigmoid weights: the sums hold weight * 2^(-m)
             __syncwarp();
             for (int sp = lane; sp < ns; sp += 32) merge_s[2 * (gh * ns + sp)] = exp2f(merge_s[2 * (gh * ns + sp)] - m) * inv;   // the chunk's weight
           }
@@ -415,6 +417,13 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) o[i][c] = 0.f;
       float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // heads 2t and 2t + 1
+      TileScores shape = plain_scores();
+      if (a.softcap > 0.f || a.score_bias) {
+        shape.shaped = true; shape.sigmoid = a.score_bias != nullptr; shape.scale = a.scale; shape.softcap = a.softcap;
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+          shape.bias[c] = (a.score_bias && 2 * t4 + c < heads) ? a.score_bias[d.kvh * G + g0 + 2 * t4 + c] : 0.f;
+      }
 
       // tile gb of this block's stream goes to warp gb mod 3 (it owns the stages gb mod `stages` can be);
       // `rank` is the warp's place among the item's tiles, which fixes the order of the merge
@@ -426,7 +435,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
         const uint32_t kt = smem_u32(stage0 + (size_t)s * STAGE_BYTES);
         const uint32_t vt = kt + TILE_BYTES;
 
-        consume_tile(kt, vt, qf, o, m_run, l_run, d.j0 + b * BK, d.k_lo, d.k_end, scale2, lane);
+        consume_tile(kt, vt, qf, o, m_run, l_run, d.j0 + b * BK, d.k_lo, d.k_end, scale2, lane, shape);
         if (g0 + 8 >= G) {           // last pass over this tile: hand the stage back
           __syncwarp();
           if (lane == 0) mbar_arrive(&empty[s]);
@@ -480,7 +489,8 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, Args a) {
             vf = v * f;
             lf = l * f + exp2f(sink2 - mf);
           }
-          a.out[(size_t)d.row * a.nh * HD + (size_t)head * HD + dd] = __float2bfloat16_rn(gated(a, vf / lf, d.row, head, dd));
+          const float y = a.score_bias ? (m == -INFINITY ? 0.f : v * exp2f(m)) : vf / lf;
+          a.out[(size_t)d.row * a.nh * HD + (size_t)head * HD + dd] = __float2bfloat16_rn(gated(a, y, d.row, head, dd));
         } else {
           a.part_o[(((size_t)d.e * a.nh + head) * a.max_splits + d.split) * HD + dd] = v;
           if (dd == 0) {
@@ -544,7 +554,9 @@ MI_API int mi_attention_decode_tma(void* out, const void* q_base, int q_stride, 
                                    const int* block_table, int bt_stride, const int* decode_items, const int* q_start,
                                    const int* ctx_len, const int* seq_slot, float* scratch, int* counters, int* status,
                                    int n_dec, int nh, int nkv, int page_size, float scale, int window, int chunk,
-                                   int max_splits, int num_sms, cudaStream_t stream, const float* sink, const void* gate, int gate_stride) {
+                                   int max_splits, int num_sms, cudaStream_t stream, const float* sink, const void* gate, int gate_stride,
+                                   float softcap, const float* score_bias) {
+  MI_REQUIRE(!(softcap < 0.f) && !(sink && score_bias), "attention_decode_tma: softcap must not be negative, and sigmoid weights take no sink");
   MI_REQUIRE(n_dec >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_decode_tma: bad head counts nh=%d nkv=%d", nh, nkv);
   MI_REQUIRE(page_size % BK == 0, "attention_decode_tma: page_size=%d must be a multiple of %d", page_size, BK);
   MI_REQUIRE(chunk >= BK && chunk % BK == 0, "attention_decode_tma: chunk=%d must be a multiple of %d", chunk, BK);
@@ -573,6 +585,7 @@ MI_API int mi_attention_decode_tma(void* out, const void* q_base, int q_stride, 
   a.gp = G < 16 ? G : 16;
   a.scale = scale;
   a.sink = sink; a.gate = (const __nv_bfloat16*)gate; a.gate_stride = gate_stride;
+  a.softcap = softcap; a.score_bias = score_bias;
   int stages = MAX_STAGES;
   while (stages > CONSUMERS && smem_bytes(stages, a.gp, max_splits, n_dec) > 220 * 1024) stages -= CONSUMERS;
   MI_REQUIRE(smem_bytes(stages, a.gp, max_splits, n_dec) <= 227 * 1024, "attention_decode_tma: shared memory does not suffice");

@@ -21,7 +21,11 @@
 // (exp(sink), unscaled, no value); an output gate multiplies the output row with sigmoid(gate[token,
 // head, :]); out_hd < head size writes only the first out_hd values of a head (padded cache rows).
 //
+// Shaped scores (attention_scores.cuh): a cap on the scaled scores, and sigmoid weights that are not normalised over the
+// keys - the score enters the online softmax as the logarithm of its weight and the output is multiplied with 2^m at the end.
+//
 // Compiled once per head size: -DMI_HEAD_DIM=<multiple of 16, 16..256>.
+#include "attention_scores.cuh"
 #include "common.cuh"
 
 #ifndef MI_HEAD_DIM
@@ -88,6 +92,8 @@ struct PrefillArgs {
   const float* sink;             // [nh] or null
   const __nv_bfloat16* gate;     // [T, gate_stride], head h at h * out_hd; or null
   int gate_stride, out_hd;
+  float scale, softcap;          // shaped scores: the scale itself and the cap (0: none)
+  const float* score_bias;       // [nh]: sigmoid weights; null: softmax
 };
 
 // Gathers keys kb*BK .. kb*BK+BK of one kv head (K and V) into a stage; rows past `last_key` are zeros.
@@ -154,6 +160,8 @@ attention_prefill_kernel(PrefillArgs a) {
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int pr[2] = {p0 + warp * 16 + g, p0 + warp * 16 + g + 8};    // positions of this thread's two rows
   const bool row_ok[2] = {warp * 16 + g < rows, warp * 16 + g + 8 < rows};
+  const bool shaped = a.softcap > 0.f || a.score_bias != nullptr, sigmoid = a.score_bias != nullptr;
+  const float head_bias = sigmoid ? a.score_bias[head] : 0.f;
 
   // ldmatrix lane addressing: lane l gives the row address of 8x8 matrix l/8, row l%8
   const int lm = lane >> 3, lr = lane & 7;
@@ -212,7 +220,7 @@ attention_prefill_kernel(PrefillArgs a) {
         const int j = kb * BK + i * 8 + 2 * t + (c & 1);
         const int h = c >> 1;
         const bool see = row_ok[h] && j <= pr[h] && (a.window <= 0 || j > pr[h] - a.window || j < a.keep_first);
-        const float v = see ? s[i][c] * a.scale_log2 : -INFINITY;
+        const float v = see ? (shaped ? mi::shaped_logit2(s[i][c], a.scale, a.softcap, sigmoid, head_bias) : s[i][c] * a.scale_log2) : -INFINITY;
         s[i][c] = v;
         mx[h] = fmaxf(mx[h], v);
       }
@@ -278,7 +286,8 @@ attention_prefill_kernel(PrefillArgs a) {
       f = exp2f(m_run[h] - m_fin);
       l = l * f + exp2f(sink2 - m_fin);
     }
-    const float inv = f / l;
+    // sigmoid weights: the sums hold weight * 2^(-m); nothing is divided by the weights' sum
+    const float inv = sigmoid ? (m_run[h] == -INFINITY ? 0.f : exp2f(m_run[h])) : f / l;
     const size_t r = (size_t)(row0 + warp * 16 + g + 8 * h);
     __nv_bfloat16* dst = a.out + (r * a.nh + head) * a.out_hd;
     const __nv_bfloat16* gt = a.gate ? a.gate + r * a.gate_stride + (size_t)head * a.out_hd : nullptr;
@@ -305,7 +314,9 @@ MI_API int mi_attention_prefill_bf16(void* out, const void* q_base, int q_stride
                                      const int* block_table, int bt_stride, const int* tiles, int n_tiles,
                                      const int* q_start, const int* q_len, const int* ctx_len, const int* seq_slot,
                                      int nh, int nkv, int page_size, float scale, int window, const float* sink,
-                                     const void* gate, int gate_stride, int out_hd, int keep_first, cudaStream_t stream) {
+                                     const void* gate, int gate_stride, int out_hd, int keep_first, float softcap,
+                                     const float* score_bias, cudaStream_t stream) {
+  MI_REQUIRE(!(softcap < 0.f) && !(sink && score_bias), "attention_prefill: softcap must not be negative, and sigmoid weights take no sink");
   MI_REQUIRE(keep_first >= 0, "attention_prefill: keep_first=%d must not be negative", keep_first);
   MI_REQUIRE(out_hd > 0 && out_hd <= HD && out_hd % 2 == 0 && gate_stride % 2 == 0, "attention_prefill: out_hd=%d must be even, up to %d", out_hd, HD);
   MI_REQUIRE(n_tiles >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0, "attention_prefill: bad head counts nh=%d nkv=%d", nh, nkv);
@@ -324,6 +335,7 @@ MI_API int mi_attention_prefill_bf16(void* out, const void* q_base, int q_stride
   a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window; a.keep_first = keep_first;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.sink = sink; a.gate = (const __nv_bfloat16*)gate; a.gate_stride = gate_stride; a.out_hd = out_hd;
+  a.scale = scale; a.softcap = softcap; a.score_bias = score_bias;
   const size_t smem = (size_t)(BQ + 4 * BK) * LDS * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured) {

@@ -96,6 +96,7 @@
 
 #include <type_traits>
 
+#include "attention_scores.cuh"
 #include "common.cuh"
 
 #ifndef MI_HEAD_DIM
@@ -170,6 +171,11 @@ struct Args {
   const float* sink;             // [nh] or null: a logit per query head whose exponential joins the denominator once
   const __nv_bfloat16* gate;     // [T, gate_stride] or null: the output is multiplied with sigmoid(gate[token, head * HD + d])
   int gate_stride;
+  // shaped scores (attention_scores.cuh): a cap on the scaled scores (0: none), and sigmoid weights with a bias per query
+  // head that are not normalised over the keys (null: softmax).  A shaped score enters the softmax as the base-2 logarithm
+  // of its weight, and the output is multiplied with 2^m at the end where the softmax divides by the sum.
+  float scale, softcap;
+  const float* score_bias;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -652,7 +658,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     const int q = warp & 3, st = warp >> 2;
     const int r = q * 32 + lane;                           // row of the block = lane of the tensor memory
     const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
-    const float sc = a.scale_log2;
+    const bool shaped = a.softcap > 0.f || a.score_bias != nullptr, sigmoid = a.score_bias != nullptr;
+    const float sc = shaped ? 1.f : a.scale_log2;          // shaped scores come as base-2 logits already
     int o_seen = 0;
     auto wait_o = [&](int upto) {
       while (o_seen <= upto) {
@@ -680,6 +687,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       const int lo_r = a.window > 0 ? max(0, pos - a.window + 1) : 0;
       float m_run = -INFINITY, l_run = 0.f;
       const int n_mine = (n - st + 1) / 2;                 // tiles of this stream
+      const float head_bias = sigmoid ? a.score_bias[head] : 0.f;
 
       for (int k = 0; k < n_mine; ++k) {
         const int j = 2 * k + st;
@@ -694,6 +702,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_issuer<CTAS>(s_free);
+        if (shaped) {
+#pragma unroll
+          for (int e = 0; e < BN; ++e) v[e] = mi::shaped_logit2(v[e], a.scale, a.softcap, sigmoid, head_bias);
+        }
         if (masked) {
           // A tile that the mask touches: the scores a row may not see are set to -inf once, here, and everything
           // after treats the tile like any other (a maximum ignores them, their exponentials are 0).  The visible
@@ -776,7 +788,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       const float l_all = fl[r] * w0 + fl[BM + r] * w1 + (a.sink ? exp2f(sink2 - m_all) : 0.f);
       constexpr int OD = HD / 2;                           // output columns of this thread
       const bool has1 = n > 1;
-      const float f0 = w0 / l_all, f1 = has1 ? w1 / l_all : 0.f;
+      // sigmoid weights: a stream's row holds weight * 2^(-m) summed over its keys; nothing is divided by the weights' sum
+      const float f0 = sigmoid ? (m0 == -INFINITY ? 0.f : exp2f(m0)) : w0 / l_all;
+      const float f1 = has1 ? (sigmoid ? (m1 == -INFINITY ? 0.f : exp2f(m1)) : w1 / l_all) : 0.f;
       (void)head; (void)row_valid;
       float o0[OD], o1[OD];
       if (has1) {
@@ -939,7 +953,9 @@ MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_
                                    const int* tiles, int n_tiles, const int* q_start, const int* q_len, const int* ctx_len,
                                    const int* seq_slot, int* status, int nh, int nkv, int page_size, float scale, int window,
                                    int num_sms, cudaStream_t stream, const int* tiles128, int n_tiles128, int pairs,
-                                   const float* sink, const void* gate, int gate_stride, int keep_first) {
+                                   const float* sink, const void* gate, int gate_stride, int keep_first, float softcap,
+                                   const float* score_bias) {
+  MI_REQUIRE(!(softcap < 0.f) && !(sink && score_bias), "attention_prefill_tc: softcap must not be negative, and sigmoid weights take no sink");
   MI_REQUIRE(keep_first >= 0, "attention_prefill_tc: keep_first=%d must not be negative", keep_first);
   MI_REQUIRE(num_sms > 0, "attention_prefill_tc: num_sms");
   MI_REQUIRE(gate == nullptr || (((uintptr_t)gate % 16) == 0 && gate_stride % 8 == 0), "attention_prefill_tc: the gate rows must be 16-byte aligned");
@@ -961,6 +977,7 @@ MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_
   a.n_tiles = n_tiles; a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window; a.keep_first = keep_first;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.sink = sink; a.gate = (const __nv_bfloat16*)gate; a.gate_stride = gate_stride;
+  a.scale = scale; a.softcap = softcap; a.score_bias = score_bias;
   CUtensorMap qm, km;
   memcpy(&qm, q_map, sizeof(qm));
   memcpy(&km, kv_map, sizeof(km));

@@ -1185,7 +1185,7 @@ def attention(out: torch.Tensor, qkv: torch.Tensor, kv_layer: torch.Tensor, bloc
   win = int(window) if window else 0
   opts.keep_first = int(keep_first) if win else 0
   even = ohd % 2 == 0 and gate_offset % 2 == 0 and gate_stride % 2 == 0
-  if qkv.dtype == torch.bfloat16 and not force_generic and head_dim % 16 == 0 and 16 <= head_dim <= 256 and even and not opts.shaped_scores():
+  if qkv.dtype == torch.bfloat16 and not force_generic and head_dim % 16 == 0 and 16 <= head_dim <= 256 and even:
     _attention_bf16(out, qkv, kv_layer, block_table, batch, num_heads, num_kv_heads, head_dim, scale, win, page_size, opts)
     return
   lib = common_lib()
@@ -1360,7 +1360,7 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
         _ptr(batch.q_len, torch.int32), _ptr(batch.ctx_len, torch.int32), _ptr(batch.seq_slot, torch.int32),
         _ptr(status, torch.int32), nh, nkv, page_size, ctypes.c_float(scale), win, _num_sms(qkv.device), _stream(),
         _ptr(wide, torch.int32) if wide is not None else _ptr(None), n_wide, pairs,
-        opts.sink_ptr(), opts.gate_ptr(), opts.gate_stride, opts.keep_first))
+        opts.sink_ptr(), opts.gate_ptr(), opts.gate_stride, opts.keep_first, ctypes.c_float(opts.softcap), opts.score_bias_ptr()))
       if batch.scratch is None and int(status[0]) != 0:
         raise KernelError("attention_prefill_tc: a bounded wait on a barrier ran out")
     else:
@@ -1369,12 +1369,13 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
         _ptr(batch.prefill_tiles, torch.int32), batch.num_prefill_tiles, _ptr(batch.q_start, torch.int32),
         _ptr(batch.q_len, torch.int32), _ptr(batch.ctx_len, torch.int32), _ptr(batch.seq_slot, torch.int32),
         nh, nkv, page_size, ctypes.c_float(scale), win, opts.sink_ptr(), opts.gate_ptr(), opts.gate_stride, opts.out_hd,
-        opts.keep_first, _stream()))
+        opts.keep_first, ctypes.c_float(opts.softcap), opts.score_bias_ptr(), _stream()))
   if batch.num_decode:
     span = min(batch.max_ctx_len, win) if win else batch.max_ctx_len
     G = nh // nkv
     tma_shapes = whole_heads and hd % 64 == 0 and page_size % 64 == 0 and os.environ.get("MINIINFER_B200_DECODE_TMA", "1") != "0"
-    cluster = decode_cluster_size(lib, hd, batch.num_decode, nkv, span) if (tma_shapes and G <= 8) else 0
+    # shaped scores (a cap, sigmoid weights) the persistent TMA kernel and the cp.async kernel know, the cluster kernel does not
+    cluster = decode_cluster_size(lib, hd, batch.num_decode, nkv, span) if (tma_shapes and G <= 8 and not opts.shaped_scores()) else 0
     if cluster:
       if batch.scratch is not None:
         status = batch.scratch.zeros("attention_decode_counters", batch.num_decode * nkv + 1, torch.int32)[:1]
@@ -1412,7 +1413,7 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
         _ptr(batch.decode_items, torch.int32), _ptr(batch.q_start, torch.int32), _ptr(batch.ctx_len, torch.int32),
         _ptr(batch.seq_slot, torch.int32), _ptr(scratch, torch.float32), _ptr(counters[1:], torch.int32), _ptr(counters[:1], torch.int32),
         batch.num_decode, nh, nkv, page_size, ctypes.c_float(scale), win, chunk, max_splits, _num_sms(qkv.device), _stream(),
-        opts.sink_ptr(), opts.gate_ptr(), opts.gate_stride))
+        opts.sink_ptr(), opts.gate_ptr(), opts.gate_stride, ctypes.c_float(opts.softcap), opts.score_bias_ptr()))
       if batch.scratch is None and int(counters[0]) != 0:
         raise KernelError("attention_decode_tma: a bounded wait on a copy barrier ran out")
     else:
@@ -1421,7 +1422,8 @@ def _attention_bf16(out, qkv, kv_layer, block_table, batch, nh, nkv, hd, scale, 
         _ptr(batch.decode_items, torch.int32), _ptr(batch.q_start, torch.int32), _ptr(batch.ctx_len, torch.int32),
         _ptr(batch.seq_slot, torch.int32), _ptr(scratch, torch.float32), _ptr(counters[1:], torch.int32),
         batch.num_decode, nh, nkv, page_size, ctypes.c_float(scale), win, chunk, max_splits,
-        opts.sink_ptr(), opts.gate_ptr(), opts.gate_stride, opts.out_hd, opts.keep_first, _stream()))
+        opts.sink_ptr(), opts.gate_ptr(), opts.gate_stride, opts.out_hd, opts.keep_first, ctypes.c_float(opts.softcap),
+        opts.score_bias_ptr(), _stream()))
 
 
 _tensor_maps: Dict[tuple, ctypes.Array] = {}

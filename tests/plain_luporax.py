@@ -195,3 +195,161 @@ def generate(cfg: dict, W: Dict[str, torch.Tensor], prompt: List[int], n: int) -
   for _ in range(n):
     ids.append(int(forward(cfg, W, ids)[-1].argmax()))
   return ids[len(prompt):]
+
+
+# ------------------------------------------------------------------------------------------ weights for the tests
+
+
+def tensor_shapes(cfg: dict) -> Dict[str, tuple]:
+  """Name -> shape of every tensor of a model with this configuration (layers that run another's weights have none)."""
+  Wd, V = cfg["width"], cfg["vocab"]
+  out: Dict[str, tuple] = {"embed": (V, Wd), "final.norm": (Wd,)}
+  for i, layer in enumerate(cfg["layers"]):
+    if layer.get("weights_of") is not None:
+      continue
+    p, m, q = f"l{i}.", layer["mixer"], f"l{i}.mix."
+    out.update({p + "norm1": (Wd,), p + "shift": (Wd,)})
+    if layer["type"] == "attention":
+      H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+      out.update({q + "q": (H * D, Wd), q + "q.b": (H * D,), q + "k": (G * D, Wd), q + "k.b": (G * D,), q + "v": (G * Dv, Wd),
+                  q + "v.b": (G * Dv,), q + "q.norm": (H * D,), q + "k.norm": (G * D,), q + "pb": (H,), q + "o": (Wd, H * Dv)})
+    elif layer["type"] == "rglru":
+      C, B, K = m["width"], m["blocks"], m["conv"]
+      out.update({q + "y": (C, Wd), q + "y.b": (C,), q + "x": (C, Wd), q + "x.b": (C,), q + "conv": (C, K), q + "conv.b": (C,),
+                  q + "ra": (B, C // B, C // B), q + "ra.b": (B, C // B), q + "ri": (B, C // B, C // B), q + "ri.b": (B, C // B),
+                  q + "lam": (C,), q + "o": (Wd, C)})
+    else:
+      C = m["width"]
+      out.update({q + "z": (C, Wd), q + "z.b": (C,), q + "x": (C, Wd), q + "x.b": (C,), q + "g": (C, Wd), q + "o": (Wd, C)})
+    mlp = layer.get("mlp")
+    if mlp is not None:
+      q, F = p + "mlp.", mlp["expert"]["ff"]
+      out[p + "norm2"] = (Wd,)
+      out[q + "router"] = (mlp["router"]["experts"], Wd)
+      for e in range(mlp["router"]["experts"]):
+        out.update({f"{q}e{e}.gate": (F, Wd), f"{q}e{e}.up": (F, Wd), f"{q}e{e}.down": (Wd, F)})
+      if mlp.get("shared") is not None:
+        S = mlp["shared"]["ff"]
+        out.update({q + "shared.gate": (S, Wd), q + "shared.up": (S, Wd), q + "shared.down": (Wd, S), q + "shared.sg": (1, Wd)})
+  return out
+
+
+def make_model(cfg: dict, seed: int) -> Dict[str, torch.Tensor]:
+  """Random weights, all exactly representable in bfloat16, under which every mechanism moves the logits: projections with
+  a fan-in scale (the experts' gate and up rows larger, so that the clamps bite), norm weights around zero, biases of the
+  size of the projections' outputs, shifts between 0 and 1, decays that keep a memory between a few and a few hundred
+  tokens, routers whose largest logits stand apart."""
+  g = torch.Generator().manual_seed(seed)
+  W: Dict[str, torch.Tensor] = {}
+  for name, shape in tensor_shapes(cfg).items():
+    last = name.split(".")[-1]
+    r = torch.randn(shape, generator=g)
+    if name == "embed":
+      t = r
+    elif last in ("norm1", "norm2") or name == "final.norm":
+      t = 0.3 * r
+    elif last == "norm":
+      t = 1.0 + 0.3 * r
+    elif last == "shift":
+      t = torch.rand(shape, generator=g)
+    elif last == "lam":
+      t = -3.5 + 1.2 * r
+    elif last == "pb":
+      t = -1.0 + 0.7 * r
+    elif last == "b":
+      t = 0.5 * r
+    elif last == "conv":
+      t = 0.5 * r
+    elif last == "router":
+      t = r * 4.0 / math.sqrt(shape[-1])
+    elif last in ("ra", "ri"):
+      t = r * 2.0 / math.sqrt(shape[-1])
+    elif last in ("gate", "up"):
+      t = r * 2.0 / math.sqrt(shape[-1])
+    else:
+      t = r * (1.5 if last in ("q", "k") else 1.0) / math.sqrt(shape[-1])
+    W[name] = t.to(torch.bfloat16).float()
+  return W
+
+
+def write_model(cfg: dict, W: Dict[str, torch.Tensor], folder: str, dtype: torch.dtype = torch.bfloat16) -> str:
+  from safetensors.torch import save_file
+  os.makedirs(folder, exist_ok=True)
+  with open(os.path.join(folder, "config.json"), "w") as f:
+    json.dump(cfg, f)
+  save_file({k: v.to(dtype).contiguous() for k, v in W.items()}, os.path.join(folder, "model.safetensors"))
+  return folder
+
+
+def make_model_dir(cfg: dict, folder: str, seed: int) -> str:
+  return write_model(cfg, make_model(cfg, seed), folder)
+
+
+def read_weights(model_dir: str) -> Dict[str, torch.Tensor]:
+  from safetensors.torch import load_file
+  return {k: v.float() for k, v in load_file(os.path.join(model_dir, "model.safetensors")).items()}
+
+
+def read_config(model_dir: str) -> dict:
+  with open(os.path.join(model_dir, "config.json"), encoding="utf-8") as f:
+    return json.load(f)
+
+
+# ------------------------------------------------------------------------------------------ configurations
+
+
+def moe(ff, limit, experts, top, shared=None) -> dict:
+  d = {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": experts, "top": top}}
+  if shared is not None:
+    d["shared"] = {"ff": shared[0], "limit": shared[1]}
+  return d
+
+
+def attention(heads, kv_heads, dim, vdim, rot_dims, base, scale, softcap, mlp, weights_of=None) -> dict:
+  m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "rot": {"dims": rot_dims, "base": base}, "scale": scale}
+  if softcap is not None:
+    m["softcap"] = softcap
+  return _layer("attention", m, mlp, weights_of)
+
+
+def rglru_layer(width, blocks, conv, mlp, weights_of=None) -> dict:
+  return _layer("rglru", {"width": width, "blocks": blocks, "conv": conv}, mlp, weights_of)
+
+
+def mingru_layer(width, mlp, weights_of=None) -> dict:
+  return _layer("mingru", {"width": width}, mlp, weights_of)
+
+
+def _layer(kind, mixer, mlp, weights_of) -> dict:
+  d = {"type": kind, "mixer": mixer, "mlp": mlp}
+  if weights_of is not None:
+    d["weights_of"] = weights_of
+  return d
+
+
+# Three configurations that differ in every size, in the order of their layers and in what is there at all.  A: a rotation
+# over a part of a head, one key/value head for four query heads, key and value sizes that differ and are no multiple of
+# 16, three parts in the recurrent unit, a layer without a feed-forward, layers that run another's weights (one of them
+# twice).  B: as many key/value heads as query heads, the whole head rotated, no cap on the scores, a recurrent unit of
+# one part whose convolution has one tap, a router that takes all of its experts and one that takes one, a feed-forward
+# without a shared expert, multipliers of 1.  C: heads of 64 (the tensor-core and tensor-copy kernels), pages of 64.
+_A_MLP = moe(24, 1.5, 5, 2, (16, 0.8))
+_C_MLP = moe(64, 2.5, 8, 3, (96, 1.2))
+CONFIGS = {
+  "A": {"architecture": "Luporax", "vocab": 300, "width": 64, "norm": {"eps": 1e-5}, "residual_mult": 0.5, "logit_scale": 0.3, "layers": [
+    mingru_layer(40, _A_MLP),
+    attention(4, 1, 24, 16, 16, 10000.0, 0.3, 20.0, _A_MLP),
+    rglru_layer(48, 3, 3, None),
+    attention(4, 1, 24, 16, 16, 10000.0, 0.3, 20.0, _A_MLP, weights_of=1),
+    rglru_layer(48, 3, 3, None, weights_of=2),
+    attention(4, 1, 24, 16, 16, 10000.0, 0.3, 20.0, _A_MLP, weights_of=3)]},
+  "B": {"architecture": "Luporax", "vocab": 200, "width": 32, "norm": {"eps": 1e-6}, "residual_mult": 1.0, "logit_scale": 1.0, "layers": [
+    rglru_layer(32, 1, 1, moe(16, 3.0, 3, 3)),
+    attention(2, 2, 16, 32, 16, 500.0, 0.25, None, moe(24, 1.0, 4, 1, (8, 2.0))),
+    mingru_layer(16, None)]},
+  "C": {"architecture": "Luporax", "vocab": 500, "width": 128, "norm": {"eps": 1e-6}, "residual_mult": 0.8, "logit_scale": 0.5, "layers": [
+    attention(8, 2, 64, 64, 32, 20000.0, 0.125, 30.0, _C_MLP),
+    rglru_layer(96, 2, 4, _C_MLP),
+    mingru_layer(160, _C_MLP),
+    attention(8, 2, 64, 64, 32, 20000.0, 0.125, 30.0, _C_MLP, weights_of=0)]},
+}
