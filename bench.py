@@ -1196,9 +1196,168 @@ def famupel_one(name: str, cfg: dict, size: dict, batch: int, steps: int, warmup
   return out
 
 
+# ---------------------------------------------------------------------------------------------- --compare luporax
+# Sizes for the comparison of the Luporax design with the closest design the engine has, Rikanex (attention with shaped
+# weights and routed experts in every layer but the first), at equal size: the sizes of the Rikanex comparison - width,
+# heads, experts (count, width, per token), layers, vocabulary.  Luporax's layers go attention, real-gated linear recurrent
+# unit, minimal gated recurrence, and again; every layer has the routed experts and a shared expert of an expert's width;
+# its attention sees every earlier token (the design has no window), Rikanex's the last 1024.
+LUPORAX_RGLRU_BLOCKS = 8
+
+
+def luporax_configs(size: dict) -> dict:
+  W, H, G, hd, L = size["width"], size["heads"], size["kv_heads"], size["head"], size["layers"]
+  mlp = {"kind": "moe", "expert": {"ff": size["expert_ff"], "limit": 7.0}, "router": {"experts": size["experts"], "top": size["top"]},
+         "shared": {"ff": size["expert_ff"], "limit": 7.0}}
+  kinds = [
+    {"type": "attention", "mlp": mlp, "mixer": {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 50.0,
+                                                "rot": {"dims": hd, "base": 500000.0}}},
+    {"type": "rglru", "mlp": mlp, "mixer": {"width": W, "blocks": LUPORAX_RGLRU_BLOCKS, "conv": 4}},
+    {"type": "mingru", "mlp": mlp, "mixer": {"width": W}},
+  ]
+  lup = {"architecture": "Luporax", "vocab": COMPARE_VOCAB, "width": W, "norm": {"eps": 1e-6}, "residual_mult": 0.7, "logit_scale": 0.25,
+         "layers": [kinds[i % 3] for i in range(L)]}
+  return {"rikanex": compare_configs(size)["rikanex"], "luporax": lup}
+
+
+def _luporax_groups(times: dict) -> dict:
+  import re
+  g = {"attention": 0.0, "experts": 0.0, "routing": 0.0, "dense_products": 0.0, "recurrence": 0.0, "block": 0.0, "other": 0.0}
+  for name, us in times.items():
+    if re.search(r"decode_tma_kernel|decode_cluster_kernel|decode_split_kernel|decode_merge|attention_prefill|attention_generic", name):
+      g["attention"] += us
+    elif "moe_gemm" in name or "moe_stream" in name or re.search(r"gemm_tc_kernel<\w+, \w+, (true|\(bool\)1)>", name):
+      g["experts"] += us
+    elif re.search(r"moe_route|moe_align|moe_combine|moe_gather", name):
+      g["routing"] += us
+    elif re.search(r"diag_recurrence|causal_conv|conv_state|gemm_batched", name):
+      g["recurrence"] += us
+    elif re.search(r"token_shift|norm_scaled_add", name):
+      g["block"] += us
+    elif "gemm_skinny" in name or "gemm_tc_kernel" in name or "gemm_stream_tc" in name or \
+        ("anonymous namespace" not in name and re.search(r"nvjet|cutlass|cublas|gemm|gemv|xmma", name, re.I)):
+      g["dense_products"] += us
+    elif not name.startswith("Memcpy") and not name.startswith("Memset"):
+      g["other"] += us
+  return g
+
+
+def luporax_one(name: str, cfg: dict, size: dict, batch: int, steps: int, warmup: int, pk: dict, kernels: bool) -> dict:
+  """Prefill and decode of one model of the comparison; with ``kernels`` the device time of its kinds of kernels and the
+  rates they reach against the measured peaks (run with dependent launch off, see main)."""
+  if name == "rikanex":
+    return compare_one(name, cfg, size, batch, steps, warmup, pk, kernels)
+  import torch
+  from miniinfer_b200.engine import StepItem
+  from miniinfer_b200.sampling import Sampler, SamplingParams
+  W, H, G, hd, L = size["width"], size["heads"], size["kv_heads"], size["head"], size["layers"]
+  T = PREFILL_TOKENS
+  with tempfile.TemporaryDirectory() as d:
+    with open(os.path.join(d, "config.json"), "w") as f:
+      json.dump(cfg, f)
+    engine = build_engine(d, batch)
+    if not kernels:
+      dec = time_decode(engine, batch, steps, warmup)
+      pre = time_prefill(engine)
+      out = {"decode_tok_s": round(dec["tok_s"], 1), "decode_ms": round(dec["ms"], 4), "launches_per_decode_step": int(dec["launches_per_step"]),
+             "prefill_tok_s": round(T / (pre["ms"] * 1e-3), 1), "prefill_ms": round(pre["ms"], 3)}
+    else:
+      rids = fill_context(engine, batch, CONTEXT, seed=1000 + batch)
+      params = [SamplingParams(temperature=0.6, max_tokens=GENERATED, ignore_eos=True)] * batch
+      tokens_dev = torch.zeros(max(batch, 1), dtype=torch.int32, device="cuda:0")
+
+      def decode(i):
+        extras = Sampler.pack(params, list(range(batch)), [i] * batch)
+        engine.runner.step_and_sample([StepItem(r, [1], (0,)) for r in rids], extras, Sampler.sample, tokens_dev,
+                                      sampling_pad=Sampler.PAD_ROWS)
+
+      for i in range(4):
+        decode(i)
+      torch.cuda.synchronize()
+      dtimes = _kernel_times(lambda i: decode(10 + i), 4)
+      dk = _luporax_groups(dtimes)
+      touched = float(size["experts"])
+      for gph in engine.runner._graphs.values():      # what the last step's last routed layer did read: the row tiles that an expert owns
+        buf = gph.ws._bufs.get(("moe_tile_expert", torch.int32))
+        if buf is not None:
+          touched = float((buf >= 0).sum().item())
+      for r in rids:
+        engine.cache.release_request(r)
+      g = torch.Generator().manual_seed(7)
+
+      def whole(i):
+        rid = f"rates{i}"
+        engine.cache.admit(rid)
+        engine.runner.step([StepItem(rid, torch.randint(0, COMPARE_VOCAB, (T,), generator=g).tolist(), (T - 1,))])
+        engine.cache.release_request(rid)
+
+      for i in range(2):
+        whole(i)
+      torch.cuda.synchronize()
+      ptimes = _kernel_times(lambda i: whole(10 + i), 2)
+      pt = _luporax_groups(ptimes)
+      for grp in (pt, dk):
+        for key in grp:
+          grp[key] = max(grp[key], 1e-9)
+      n_att, n_rg, n_mg = (L + 2) // 3, (L + 1) // 3, L // 3
+      E, F, top = size["experts"], size["expert_ff"], size["top"]
+      attn_flops = n_att * 4.0 * H * hd * sum(t + 1 for t in range(T))
+      attn_bytes = batch * CONTEXT * n_att * 2 * G * hd * 2
+      moe_flops = L * T * top * 3 * 2.0 * F * W
+      moe_bytes = L * touched * 3 * F * W * 2
+      proj_w = n_att * ((H + 2 * G) * hd * W + W * H * hd) + n_rg * 3 * W * W + n_mg * 4 * W * W
+      shared_w = L * 3 * F * W
+      dense_w = proj_w + shared_w + COMPARE_VOCAB * W
+      # what the recurrent layers must move a token besides their dense products: the convolution (x in, u out), the gates'
+      # batched product (u in, two float32 logits a channel out) and the recurrence (u, logits, y in, the read-out out) of an
+      # rglru layer - 28 bytes a channel -, z, x, g in and the read-out out of a mingru layer - 8 bytes a channel; in a decode
+      # step also every request's states in and out (4 bytes a value; the convolution keeps three earlier inputs a channel)
+      rec_io = n_rg * 28 * W + n_mg * 8 * W
+      rec_state = (n_rg * 4 * W + n_mg * W) * 4 * 2
+      gates_flops = n_rg * T * 2.0 * 2 * W * (W // LUPORAX_RGLRU_BLOCKS)
+      # the blocks: a sublayer reads the float32 row and writes its rounding (the mixer's through the shift), then reads the
+      # sublayer's output and the row and writes the row (and its rounding for the next sublayer)
+      block_bytes = L * ((4 + 2) * W + (2 + 4 + 4 + 2) * W + (2 + 4 + 4) * W)
+      out = {"prefill_attention": {"us": round(pt["attention"], 1), "TFLOP/s": round(attn_flops / pt["attention"] / 1e6, 1),
+                                   "frac": round(attn_flops / pt["attention"] / 1e6 / pk["bf16_tflops"], 4)},
+             "decode_attention": {"us": round(dk["attention"], 1), "GB/s": round(attn_bytes / dk["attention"] / 1e3, 1),
+                                  "frac": round(attn_bytes / dk["attention"] / 1e3 / pk["hbm_gbs"], 4)},
+             "prefill_experts": {"us": round(pt["experts"], 1), "TFLOP/s": round(moe_flops / pt["experts"] / 1e6, 1),
+                                 "frac": round(moe_flops / pt["experts"] / 1e6 / pk["bf16_tflops"], 4)},
+             "decode_experts": {"us": round(dk["experts"], 1), "GB/s": round(moe_bytes / dk["experts"] / 1e3, 1),
+                                "frac": round(moe_bytes / dk["experts"] / 1e3 / pk["hbm_gbs"], 4), "experts_read_per_layer": round(touched, 1)},
+             "routing_us": {"prefill": round(pt["routing"], 1), "decode": round(dk["routing"], 1)},
+             "prefill_dense_products": {"us": round(pt["dense_products"], 1),
+                                        "TFLOP/s": round(2.0 * T * (proj_w + shared_w) / pt["dense_products"] / 1e6, 1),
+                                        "frac": round(2.0 * T * (proj_w + shared_w) / pt["dense_products"] / 1e6 / pk["bf16_tflops"], 4)},
+             "decode_dense_products": {"us": round(dk["dense_products"], 1), "GB/s": round(2.0 * dense_w / dk["dense_products"] / 1e3, 1),
+                                       "frac": round(2.0 * dense_w / dk["dense_products"] / 1e3 / pk["hbm_gbs"], 4)},
+             "prefill_recurrence": {"us": round(pt["recurrence"], 1), "GB/s": round(T * rec_io / pt["recurrence"] / 1e3, 1),
+                                    "frac": round(T * rec_io / pt["recurrence"] / 1e3 / pk["hbm_gbs"], 4),
+                                    "gates_GFLOP": round(gates_flops / 1e9, 2)},
+             "decode_recurrence": {"us": round(dk["recurrence"], 1), "GB/s": round(batch * (rec_io + rec_state) / dk["recurrence"] / 1e3, 1),
+                                   "frac": round(batch * (rec_io + rec_state) / dk["recurrence"] / 1e3 / pk["hbm_gbs"], 4)},
+             "prefill_block": {"us": round(pt["block"], 1), "GB/s": round(T * block_bytes / pt["block"] / 1e3, 1),
+                               "frac": round(T * block_bytes / pt["block"] / 1e3 / pk["hbm_gbs"], 4)},
+             "decode_block_us": round(dk["block"], 1),
+             "other_us": {"prefill": round(pt["other"], 1), "decode": round(dk["other"], 1)}}
+
+      def top_of(times):
+        rows = sorted(((us, n) for n, us in times.items() if not n.startswith("Mem")), reverse=True)[:14]
+        return [[round(us, 1), n.replace("(anonymous namespace)::", "")[:70]] for us, n in rows]
+
+      out["top_kernels_us"] = {"prefill": top_of(ptimes), "decode": top_of(dtimes)}
+    engine.stop()
+    del engine
+    gc.collect()
+    torch.cuda.empty_cache()
+  return out
+
+
 def compare_designs(args) -> int:
   """``--compare rikanex`` / ``--compare vugudra``: the design beside the Qwen3 dense decoder at equal sizes (random weights);
-  ``--compare famupel``: the design beside Vugudra, the closest of the engine's designs, at equal sizes: prefill of
+  ``--compare famupel``: the design beside Vugudra, ``--compare luporax``: the design beside Rikanex, each the closest of
+  the engine's designs, at equal sizes: prefill of
   one 2048-token prompt and decode steps at ``--batch`` requests with ``--context``-token contexts, and, from a process of
   its own with dependent launch off, what the kinds of kernels of both reach against the measured peaks."""
   pk = peaks()
@@ -1209,8 +1368,9 @@ def compare_designs(args) -> int:
   sizes = [x for x in args.sizes.split(",") if x]
   design = args.compare
   sizes_of, configs_of, one = {"rikanex": (COMPARE_SIZES, compare_configs, compare_one), "vugudra": (VUGUDRA_SIZES, vugudra_configs, vugudra_one),
-                               "famupel": (FAMUPEL_SIZES, famupel_configs, famupel_one)}[design]
-  beside = "vugudra" if design == "famupel" else "qwen3"
+                               "famupel": (FAMUPEL_SIZES, famupel_configs, famupel_one),
+                               "luporax": (COMPARE_SIZES, luporax_configs, luporax_one)}[design]
+  beside = {"famupel": "vugudra", "luporax": "rikanex"}.get(design, "qwen3")
   result = {"compare": f"{design} beside {beside} at equal sizes", "batch": args.batch, "context": CONTEXT, "window": COMPARE_WINDOW,
             "vocab": COMPARE_VOCAB, "prefill_tokens": PREFILL_TOKENS, "steps": args.steps, "warmup": warmup, "dtype": "bf16",
             "data": "synthetic: random weights, uniform random token ids", "peaks": pk["source"], "sizes": {}}
@@ -1249,8 +1409,8 @@ def main() -> int:
   ap.add_argument("--steps", type=int, default=128)
   ap.add_argument("--warmup", type=int, default=8)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-child", "kernels-child", "compare-child"])
-  ap.add_argument("--compare", default=None, choices=["rikanex", "vugudra", "famupel"],
-                  help="time the Rikanex or the Vugudra design beside the Qwen3 dense decoder, or the Famupel design beside Vugudra, at equal sizes (--sizes), print one JSON line and exit")
+  ap.add_argument("--compare", default=None, choices=["rikanex", "vugudra", "famupel", "luporax"],
+                  help="time the Rikanex or the Vugudra design beside the Qwen3 dense decoder, the Famupel design beside Vugudra, or the Luporax design beside Rikanex, at equal sizes (--sizes), print one JSON line and exit")
   ap.add_argument("--sizes", default="s,m,l", help="with --compare: which of the sizes s, m, l (commas between them)")
   ap.add_argument("--batch", type=int, default=8)
   ap.add_argument("--shape", default="0.6b", choices=sorted(SHAPES), help="layer sizes: the default, or another Qwen3 model's")

@@ -92,16 +92,17 @@ norm_scaled_add_kernel(float* __restrict__ resid, const TY* __restrict__ y, cons
 template <typename T>
 struct RglruCell {
   const T* u; int ldu;              // the convolved x branch [tokens, C]
-  const float* gates; int ldg;      // [tokens, blocks, 2 * bw]: a block's r logits, then its i logits
+  const float* gates; int ldg;      // a part's r logits, then its i logits: part b of token t at t * ldg + b * part_stride
+  long long part_stride;            // 2 * bw for [tokens, parts, 2 bw]; tokens * 2 bw (with ldg = 2 bw) for [parts, tokens, 2 bw]
   const T* y; int ldy;              // the y branch as projected [tokens, C]
   const float *r_bias, *i_bias, *y_bias, *lam;
   int bw;
   // per channel, set by prepare()
-  float rb, ib, yb, rate; int goff;
+  float rb, ib, yb, rate; long long goff;
   __device__ __forceinline__ void prepare(int c) {
     rb = r_bias[c]; ib = i_bias[c]; yb = y_bias ? y_bias[c] : 0.f;
     rate = -8.f * softplus_f(lam[c]);
-    goff = (c / bw) * 2 * bw + c % bw;
+    goff = (long long)(c / bw) * part_stride + c % bw;
   }
   __device__ __forceinline__ void ab(int row, int c, float& a, float& b) const {
     const float* g = gates + (size_t)row * ldg + goff;
@@ -236,10 +237,11 @@ MI_API int mi_norm_scaled_add(float* resid, const void* y, int y_dtype, const fl
 
 MI_API int mi_recurrence_segment_warps() { return REC_NW; }
 
-// out, u, y: [T, C] in dtype with row strides; gates [T, blocks, 2 * (C / blocks)] float32 with row stride ldg; biases and lam [C]
-// float32 (y_bias may be null); state rows float32 of at least C values.  segmented: the form with stretches side by side,
+// out, u, y: [T, C] in dtype with row strides; gates float32: the 2 * (C / blocks) logits of part b of token t (r, then i) start at
+// t * ldg + b * part_stride, so [T, blocks, .] and [blocks, T, .] both go; biases and lam [C] float32 (y_bias may be null);
+// state rows float32 of at least C values.  segmented: the form with stretches side by side,
 // taken by the items of at least seg_min * (warps of a block) new tokens.
-MI_API int mi_rglru_recurrence(void* out, int ldo, const void* u, int ldu, const float* gates, int ldg, const void* y, int ldy, int dtype,
+MI_API int mi_rglru_recurrence(void* out, int ldo, const void* u, int ldu, const float* gates, int ldg, long long part_stride, const void* y, int ldy, int dtype,
                                const float* r_bias, const float* i_bias, const float* y_bias, const float* lam, float* state,
                                long long state_stride, const int* q_start, const int* q_len, const int* seq_slot, int items, int C,
                                int blocks, int segmented, int seg_min, cudaStream_t stream) {
@@ -247,10 +249,10 @@ MI_API int mi_rglru_recurrence(void* out, int ldo, const void* u, int ldu, const
   MI_REQUIRE(state_stride >= C && seg_min >= 1, "rglru: the state rows are too short");
   if (items == 0) return 0;
   if (dtype == MI_BF16) {
-    RglruCell<__nv_bfloat16> cell{(const __nv_bfloat16*)u, ldu, gates, ldg, (const __nv_bfloat16*)y, ldy, r_bias, i_bias, y_bias, lam, C / blocks};
+    RglruCell<__nv_bfloat16> cell{(const __nv_bfloat16*)u, ldu, gates, ldg, part_stride, (const __nv_bfloat16*)y, ldy, r_bias, i_bias, y_bias, lam, C / blocks};
     launch_recurrence<__nv_bfloat16>(cell, (__nv_bfloat16*)out, ldo, state, state_stride, q_start, q_len, seq_slot, items, C, segmented, seg_min, stream);
   } else if (dtype == MI_F32) {
-    RglruCell<float> cell{(const float*)u, ldu, gates, ldg, (const float*)y, ldy, r_bias, i_bias, y_bias, lam, C / blocks};
+    RglruCell<float> cell{(const float*)u, ldu, gates, ldg, part_stride, (const float*)y, ldy, r_bias, i_bias, y_bias, lam, C / blocks};
     launch_recurrence<float>(cell, (float*)out, ldo, state, state_stride, q_start, q_len, seq_slot, items, C, segmented, seg_min, stream);
   } else {
     return mi_fail("rglru: unknown dtype %d", dtype);

@@ -247,6 +247,9 @@ def linear(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, force_skinny: bo
       if out.dtype == torch.bfloat16:
         torch.mm(x, _transposed(w), out=out)
         return
+      if _mm_f32_out_works(out.device):
+        torch.mm(x, _transposed(w), out_dtype=torch.float32, out=out)
+        return
     linear_batched(out.unsqueeze(1), x.unsqueeze(1), w.unsqueeze(0))
     return
   if x.dtype == torch.float32:
@@ -750,21 +753,25 @@ def _state_rows_arg(state: torch.Tensor, width: int, what: str):
 
 def rglru_recurrence(out: torch.Tensor, u: torch.Tensor, gates: torch.Tensor, y: torch.Tensor, r_bias: torch.Tensor, i_bias: torch.Tensor,
                      y_bias: Optional[torch.Tensor], lam: torch.Tensor, state: torch.Tensor, ctx, blocks: int) -> None:
-  """The real-gated linear recurrent unit over the channels of ``u [T, C]``: with ``gates [T, blocks, 2 C / blocks]`` float32 (a
-  block's logits of r, then of i), ``r = sigmoid(. + r_bias)``, ``i = sigmoid(. + i_bias)``, ``a = exp(-8 r softplus(lam))``,
+  """The real-gated linear recurrent unit over the channels of ``u [T, C]``: with ``gates`` float32, ``[T, 2 C]`` (token after
+  token, part after part) or ``[blocks, T, 2 C / blocks]`` (part after part, as one product a part leaves them) - a
+  part's logits of r, then of i -, ``r = sigmoid(. + r_bias)``, ``i = sigmoid(. + i_bias)``, ``a = exp(-8 r softplus(lam))``,
   ``S <- a S + sqrt(1 - a^2) i u`` from the item's row of ``state``, and ``out = S * gelu_tanh(y + y_bias)``.  ``u``, ``y``, ``out``
   may be column ranges of wider rows; biases and ``lam`` are float32 ``[C]``."""
   lib = common_lib()
   T, C = u.shape
-  if (out.shape != (T, C) or y.shape != (T, C) or gates.shape != (T, 2 * C) or gates.dtype != torch.float32 or not gates.is_contiguous()
-      or out.dtype != u.dtype or y.dtype != u.dtype or C % blocks):
+  if (out.shape != (T, C) or y.shape != (T, C) or gates.dtype != torch.float32 or not gates.is_contiguous()
+      or out.dtype != u.dtype or y.dtype != u.dtype or C % blocks or tuple(gates.shape) not in ((T, 2 * C), (blocks, T, 2 * C // blocks))):
     raise KernelError("rglru_recurrence: shapes or dtypes do not match")
+  by_part = gates.dim() == 3
+  ldg, part_stride = (2 * C // blocks, T * 2 * C // blocks) if by_part else (2 * C, 2 * C // blocks)
   for b in (r_bias, i_bias, lam) + ((y_bias,) if y_bias is not None else ()):
     if b.shape != (C,) or b.dtype != torch.float32:
       raise KernelError("rglru_recurrence: biases and lam are one float32 per channel")
   (op, ldo), (up, ldu), (yp, ldy) = _cols(out, "rglru_recurrence"), _cols(u, "rglru_recurrence"), _cols(y, "rglru_recurrence")
   sp, ss = _state_rows_arg(state, C, "rglru_recurrence")
-  _check(lib, lib.mi_rglru_recurrence(op, ldo, up, ldu, _ptr(gates, torch.float32), 2 * C, yp, ldy, _dt(u), _ptr(r_bias, torch.float32),
+  _check(lib, lib.mi_rglru_recurrence(op, ldo, up, ldu, _ptr(gates, torch.float32), ldg, ctypes.c_longlong(part_stride), yp, ldy, _dt(u),
+                                      _ptr(r_bias, torch.float32),
                                       _ptr(i_bias, torch.float32), _ptr(y_bias, torch.float32) if y_bias is not None else _ptr(None),
                                       _ptr(lam, torch.float32), sp, ss, _ptr(ctx.q_start, torch.int32), _ptr(ctx.q_len, torch.int32),
                                       _ptr(ctx.seq_slot, torch.int32), ctx.num_items, C, blocks, _recurrence_segmented(u.dtype, ctx),

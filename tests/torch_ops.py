@@ -234,7 +234,7 @@ def norm_scaled_add(resid, y, weight, eps, mult, ctx, copy=None, keep=None):
 def rglru_recurrence(out, u, gates, y, r_bias, i_bias, y_bias, lam, state, ctx, blocks):
   T, C = u.shape
   P = C // blocks
-  g = gates.view(T, blocks, 2 * P)
+  g = gates.transpose(0, 1) if gates.dim() == 3 else gates.view(T, blocks, 2 * P)
   r = torch.sigmoid(g[:, :, :P].reshape(T, C) + r_bias)
   i = torch.sigmoid(g[:, :, P:].reshape(T, C) + i_bias)
   log_a = -8.0 * r * torch.nn.functional.softplus(lam)
