@@ -42,3 +42,32 @@ MI_API int mi_gemm_cublas_bf16(void* out, int out_dtype, const void* x, const vo
   if (st != CUBLAS_STATUS_SUCCESS) return mi_fail("gemm_cublas: cublasGemmEx failed with status %d (M=%d N=%d K=%d)", (int)st, M, N, K);
   return 0;
 }
+
+// The same for `batch` products side by side: out[b][M, N] = x[b][M, K] * w[b][N, K]^T with x[b] = x + b * x_batch (a column
+// range of wider rows when x_batch < lda), w[b] = w + b * w_batch, out[b] = out + b * out_batch, packed rows of out and w.
+// The parts of a block-diagonal map in one call.
+MI_API int mi_gemm_cublas_bf16_batched(void* out, int out_dtype, const void* x, const void* w, int M, int N, int K, int lda,
+                                       long long x_batch, long long w_batch, long long out_batch, int batch, cudaStream_t stream) {
+  MI_REQUIRE(M >= 0 && N > 0 && K > 0 && lda >= K && batch > 0, "gemm_cublas_batched: bad sizes M=%d N=%d K=%d lda=%d batch=%d", M, N, K, lda, batch);
+  MI_REQUIRE(out_dtype == MI_BF16 || out_dtype == MI_F32, "gemm_cublas_batched: unknown output dtype %d", out_dtype);
+  if (M == 0) return 0;
+  int dev = 0;
+  cudaError_t ce = cudaGetDevice(&dev);
+  MI_REQUIRE(ce == cudaSuccess && dev >= 0 && dev < MAX_DEVICES, "gemm_cublas_batched: no current device");
+  if (!handles[dev]) {
+    cublasStatus_t st = cublasCreate(&handles[dev]);
+    if (st != CUBLAS_STATUS_SUCCESS) {
+      handles[dev] = nullptr;
+      return mi_fail("gemm_cublas_batched: cublasCreate failed with status %d", (int)st);
+    }
+  }
+  cublasHandle_t h = handles[dev];
+  cublasStatus_t st = cublasSetStream(h, stream);
+  if (st != CUBLAS_STATUS_SUCCESS) return mi_fail("gemm_cublas_batched: cublasSetStream failed with status %d", (int)st);
+  const float alpha = 1.f, beta = 0.f;
+  st = cublasGemmStridedBatchedEx(h, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha, w, CUDA_R_16BF, K, w_batch, x, CUDA_R_16BF, lda, x_batch, &beta,
+                                  out, out_dtype == MI_BF16 ? CUDA_R_16BF : CUDA_R_32F, N, out_batch, batch, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
+  if (st != CUBLAS_STATUS_SUCCESS)
+    return mi_fail("gemm_cublas_batched: cublasGemmStridedBatchedEx failed with status %d (M=%d N=%d K=%d batch=%d)", (int)st, M, N, K, batch);
+  return 0;
+}

@@ -14,6 +14,21 @@ MI_API int mi_gemm_skinny_swiglu_bf16(void* out, const void* x, const void* w, i
   return dispatch_swiglu((__nv_bfloat16*)out, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, M, I, K, ldo, stream);
 }
 
+// The same for up to 16 rows with another gated activation (a MiGlu of common.cuh) in the epilogue.
+MI_API int mi_gemm_skinny_glu_bf16(void* out, const void* x, const void* w, int M, int I, int K, int ldo, int glu, float limit,
+                                   cudaStream_t stream) {
+  MI_REQUIRE(M >= 0 && M <= 16, "gemm_skinny_glu: M=%d is not in 0..16", M);
+  MI_REQUIRE(I > 0 && K > 0 && ldo >= I, "gemm_skinny_glu: bad sizes I=%d K=%d ldo=%d", I, K, ldo);
+  MI_REQUIRE(K % 8 == 0, "gemm_skinny_glu: K=%d must be a multiple of 8 (16-byte loads of bf16 rows)", K);
+  MI_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0, "gemm_skinny_glu: operands must be 16-byte aligned");
+  MI_REQUIRE(glu == MI_GLU_SILU || (glu == MI_GLU_CLAMPED && limit > 0.f), "gemm_skinny_glu: unknown activation %d or a limit that is not positive", glu);
+  if (M == 0) return 0;
+  FuseArgs fa{nullptr, nullptr, 0.f};
+  fa.glu = glu;
+  fa.limit = limit;
+  return dispatch_swiglu16<FUSE_NONE>((__nv_bfloat16*)out, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, M, I, K, ldo, stream, fa);
+}
+
 MI_API int mi_gemm_skinny_bf16(void* out, int out_dtype, const void* x, const void* w, int M, int N, int K,
                                int ldo, cudaStream_t stream) {
   MI_REQUIRE(M >= 0 && M <= 64, "gemm_skinny: M=%d is not in 0..64 (use the large-M product)", M);

@@ -95,9 +95,9 @@ __device__ __forceinline__ uint4 normed8(const float* x, const float* w, float r
 // the 8 up rows of the same columns, and the result is silu(gate) * up of the bf16-rounded products,
 // as the product followed by the activation kernel rounds them.
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-__device__ __forceinline__ float swiglu(float gate, float up) {
+__device__ __forceinline__ float swiglu(float gate, float up, int glu, float limit) {
   const float g = round_bf16(gate), u = round_bf16(up);
-  return mi::silu_mul_fast(g, u);
+  return mi::glu_fast(g, u, glu, limit);      // MI_GLU_SILU: silu(g) * u; the other gated activations of common.cuh alike
 }
 
 // What may be fused to the product (FUSE; MT == 1 only, the decode step's products):
@@ -115,6 +115,8 @@ struct FuseArgs {
   const float* xf;       // FUSE_NORM: residual rows [M, K]
   const float* norm_w;   // FUSE_NORM: norm weights [K]
   float eps;
+  int glu = 0;           // SWIGLU: the gated activation (a MiGlu of common.cuh) and its limit
+  float limit = 0.f;
 };
 
 template <int MT, int NT, int KSPLIT, bool HALF, typename TOut, bool SWIGLU = false, int W = WARPS, int FUSE = FUSE_NONE>
@@ -247,7 +249,7 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int m = i * 16 + g + 8 * (c >> 1), n = n0 + 2 * t + (c & 1);
-          if (m < rows && n < N) put_out<FUSE, TOut>(out + (size_t)m * ldo + n, swiglu(acc[i][0][c], acc[i][NT - 1][c]));
+          if (m < rows && n < N) put_out<FUSE, TOut>(out + (size_t)m * ldo + n, swiglu(acc[i][0][c], acc[i][NT - 1][c], fa.glu, fa.limit));
         }
       return;
     }
@@ -285,7 +287,7 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
       s += tile[c];
       if (SWIGLU) s_up += tile[8 + c];
     }
-    put_out<FUSE, TOut>(out + (size_t)m * ldo + n, SWIGLU ? swiglu(s, s_up) : s);
+    put_out<FUSE, TOut>(out + (size_t)m * ldo + n, SWIGLU ? swiglu(s, s_up, fa.glu, fa.limit) : s);
   }
 }
 

@@ -61,6 +61,22 @@ qkv_prepare_kernel(PrepArgs<T> a) {
   const T* row = a.proj + (size_t)tkn * a.proj_stride;
   const int units = a.nh + 2 * a.nkv;
   const int page = slot >= 0 ? slot / a.page_size : 0, off = slot >= 0 ? slot % a.page_size : 0;
+  // The norm over the whole projection: the block adds up the squares of all of the token's queries, then of all its keys,
+  // once for its four heads - every block of the token the same squares in the same order, which depends on the sizes alone.
+  float r_whole[2] = {1.f, 1.f};
+  if (a.normalise && a.norm_whole) {
+    __shared__ float scratch[33];
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      const int n = (which ? a.nkv : a.nh) * a.dim, c0 = which ? a.k_off : a.q_off;
+      float sw = 0.f;
+      for (int d = threadIdx.x; d < n; d += PREP_WARPS * 32) {
+        const float x = mi::to_float(row[c0 + d]) + (a.bias ? a.bias[c0 + d] : 0.f);
+        sw = fmaf(x, x, sw);
+      }
+      r_whole[which] = 1.f / sqrtf(mi::block_sum(sw, scratch) / (float)n + a.eps);
+    }
+  }
   for (int u = blockIdx.y * PREP_WARPS + warp; u < units; u += PREP_WARPS * gridDim.y) {
     if (u < a.nh + a.nkv) {
       // a query head or a key head
@@ -80,16 +96,8 @@ qkv_prepare_kernel(PrepArgs<T> a) {
         ss += v[i] * v[i];
       }
       float r = 1.f;
-      if (a.normalise && a.norm_whole) {
-        // every warp of the token's queries (keys) adds up the same squares in the same order
-        const int n = (is_q ? a.nh : a.nkv) * a.dim, c0 = is_q ? a.q_off : a.k_off;
-        float sw = 0.f;
-        for (int d = lane; d < n; d += 32) {
-          const float x = mi::to_float(row[c0 + d]) + (a.bias ? a.bias[c0 + d] : 0.f);
-          sw = fmaf(x, x, sw);
-        }
-        r = 1.f / sqrtf(mi::warp_sum(sw) / (float)n + a.eps);
-      } else if (a.normalise) r = 1.f / sqrtf(mi::warp_sum(ss) / (float)a.dim + a.eps);
+      if (a.normalise && a.norm_whole) r = r_whole[is_q ? 0 : 1];
+      else if (a.normalise) r = 1.f / sqrtf(mi::warp_sum(ss) / (float)a.dim + a.eps);
       T* dst = nullptr;
       if (is_q) dst = a.q_out + ((size_t)tkn * a.nh + h) * a.hdp;
       else if (slot >= 0) dst = a.kv_layer + ((((size_t)page * 2 + 0) * a.nkv + h) * a.page_size + off) * a.hdp;

@@ -521,6 +521,28 @@ def linear_batched(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, bias: Op
     int(bool(softplus)), ctypes.c_void_p(row_gate.data_ptr()) if row_gate is not None else _ptr(None), gate_stride, _stream()))
 
 
+def linear_parts(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> None:
+  """A block-diagonal map: ``out[b] = x[:, b K:(b + 1) K] @ w[b]^T`` for ``x [M, parts * K]``, ``w [parts, N, K]`` and
+  ``out [parts, M, N]`` (bfloat16 or float32), all contiguous.  bfloat16 with more than 16 rows: one strided batched library
+  product on the tensor cores (a library product a part while a graph is recorded); else the batched FMA kernels."""
+  B, N, K = w.shape
+  M = x.shape[0]
+  if x.shape != (M, B * K) or out.shape != (B, M, N) or x.dtype != w.dtype or not (x.is_contiguous() and w.is_contiguous() and out.is_contiguous()):
+    raise KernelError(f"linear_parts: shapes do not match: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+  if M == 0:
+    return
+  if x.dtype == torch.bfloat16 and M > SKINNY_BEST_M and K % 8 == 0 and out.dtype in (torch.bfloat16, torch.float32):
+    if not _capturing:
+      lib = common_lib()
+      _check(lib, lib.mi_gemm_cublas_bf16_batched(_ptr(out), _dt(out), _ptr(x), _ptr(w), M, N, K, B * K, ctypes.c_longlong(K),
+                                                  ctypes.c_longlong(N * K), ctypes.c_longlong(M * N), B, _stream()), kernels=0)
+      return
+    for b in range(B):
+      linear(out[b], x[:, b * K:(b + 1) * K], w[b])
+    return
+  linear_batched(out.transpose(0, 1), x.view(M, B, K), w)
+
+
 def causal_conv(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
                 ctx, silu: bool = True, in_bias: Optional[torch.Tensor] = None) -> None:
   """Short causal convolution over time per channel with the activation behind it, continuing from and updating the
@@ -751,13 +773,21 @@ def _state_rows_arg(state: torch.Tensor, width: int, what: str):
   return ctypes.c_void_p(state.data_ptr()), ctypes.c_longlong(state.stride(0))
 
 
+def _recurrence_scratch(workspace, segmented: int, T: int, C: int):
+  """Scratch of the segmented form: what the tokens give the channels, prepared by a kernel of its own."""
+  if not segmented or workspace is None:
+    return 0, _ptr(None)
+  return T, _ptr(workspace.buffer("recurrence_prepared", (3 * T * C,), torch.float32))
+
+
 def rglru_recurrence(out: torch.Tensor, u: torch.Tensor, gates: torch.Tensor, y: torch.Tensor, r_bias: torch.Tensor, i_bias: torch.Tensor,
-                     y_bias: Optional[torch.Tensor], lam: torch.Tensor, state: torch.Tensor, ctx, blocks: int) -> None:
+                     y_bias: Optional[torch.Tensor], lam: torch.Tensor, state: torch.Tensor, ctx, blocks: int, workspace=None) -> None:
   """The real-gated linear recurrent unit over the channels of ``u [T, C]``: with ``gates`` float32, ``[T, 2 C]`` (token after
   token, part after part) or ``[blocks, T, 2 C / blocks]`` (part after part, as one product a part leaves them) - a
   part's logits of r, then of i -, ``r = sigmoid(. + r_bias)``, ``i = sigmoid(. + i_bias)``, ``a = exp(-8 r softplus(lam))``,
   ``S <- a S + sqrt(1 - a^2) i u`` from the item's row of ``state``, and ``out = S * gelu_tanh(y + y_bias)``.  ``u``, ``y``, ``out``
-  may be column ranges of wider rows; biases and ``lam`` are float32 ``[C]``."""
+  may be column ranges of wider rows; biases and ``lam`` are float32 ``[C]``.  ``workspace`` lends the scratch of the form
+  with stretches side by side (long bfloat16 portions)."""
   lib = common_lib()
   T, C = u.shape
   if (out.shape != (T, C) or y.shape != (T, C) or gates.dtype != torch.float32 or not gates.is_contiguous()
@@ -770,16 +800,18 @@ def rglru_recurrence(out: torch.Tensor, u: torch.Tensor, gates: torch.Tensor, y:
       raise KernelError("rglru_recurrence: biases and lam are one float32 per channel")
   (op, ldo), (up, ldu), (yp, ldy) = _cols(out, "rglru_recurrence"), _cols(u, "rglru_recurrence"), _cols(y, "rglru_recurrence")
   sp, ss = _state_rows_arg(state, C, "rglru_recurrence")
+  segmented = _recurrence_segmented(u.dtype, ctx)
+  rows, scratch = _recurrence_scratch(workspace, segmented, T, C)
   _check(lib, lib.mi_rglru_recurrence(op, ldo, up, ldu, _ptr(gates, torch.float32), ldg, ctypes.c_longlong(part_stride), yp, ldy, _dt(u),
                                       _ptr(r_bias, torch.float32),
                                       _ptr(i_bias, torch.float32), _ptr(y_bias, torch.float32) if y_bias is not None else _ptr(None),
                                       _ptr(lam, torch.float32), sp, ss, _ptr(ctx.q_start, torch.int32), _ptr(ctx.q_len, torch.int32),
-                                      _ptr(ctx.seq_slot, torch.int32), ctx.num_items, C, blocks, _recurrence_segmented(u.dtype, ctx),
-                                      RECURRENCE_SEGMENT_MIN, _stream()))
+                                      _ptr(ctx.seq_slot, torch.int32), ctx.num_items, C, blocks, segmented,
+                                      RECURRENCE_SEGMENT_MIN, rows, scratch, _stream()), kernels=2 if rows else 1)
 
 
 def mingru_recurrence(out: torch.Tensor, proj: torch.Tensor, z_bias: Optional[torch.Tensor], x_bias: Optional[torch.Tensor],
-                      state: torch.Tensor, ctx) -> None:
+                      state: torch.Tensor, ctx, workspace=None) -> None:
   """The minimal gated recurrence over ``proj [T, 3 C]`` (logits of z, then x, then g): ``z = sigmoid(. + z_bias)``, the candidate
   ``c = x + 1/2`` where ``x = . + x_bias >= 0`` and ``sigmoid(x)`` below, ``S <- (1 - z) S + z c`` from the item's row of ``state``,
   ``out = S * silu(g)``."""
@@ -792,10 +824,13 @@ def mingru_recurrence(out: torch.Tensor, proj: torch.Tensor, z_bias: Optional[to
       raise KernelError("mingru_recurrence: biases are one float32 per channel")
   (op, ldo), (pp, ld) = _cols(out, "mingru_recurrence"), _cols(proj, "mingru_recurrence")
   sp, ss = _state_rows_arg(state, C, "mingru_recurrence")
+  segmented = _recurrence_segmented(out.dtype, ctx)
+  rows, scratch = _recurrence_scratch(workspace, segmented, T, C)
   _check(lib, lib.mi_mingru_recurrence(op, ldo, pp, ld, _dt(out), _ptr(z_bias, torch.float32) if z_bias is not None else _ptr(None),
                                        _ptr(x_bias, torch.float32) if x_bias is not None else _ptr(None), sp, ss,
                                        _ptr(ctx.q_start, torch.int32), _ptr(ctx.q_len, torch.int32), _ptr(ctx.seq_slot, torch.int32),
-                                       ctx.num_items, C, _recurrence_segmented(out.dtype, ctx), RECURRENCE_SEGMENT_MIN, _stream()))
+                                       ctx.num_items, C, segmented, RECURRENCE_SEGMENT_MIN, rows, scratch, _stream()),
+         kernels=2 if rows else 1)
 
 
 def hyper_connection(res: torch.Tensor, streams: torch.Tensor, y: Optional[torch.Tensor], mix: Optional[torch.Tensor],
@@ -909,6 +944,7 @@ def latent_query(q: torch.Tensor, q_out: torch.Tensor, heads: int, dim: int, rot
                                   _ptr(positions, torch.int32), int(bool(interleaved)), _stream()))
 
 
+ROUTER_KERNEL_MAX_COLUMNS = 64   # up to this many router rows the logits of many tokens come from a kernel of this package
 MOE_TC_ROW_TILE = 256            # rows of a stretch of the tcgen05 grouped product: what a pair of blocks takes at a time
 MOE_TC_MIN_ROWS_PER_EXPERT = 128   # from this many (token, choice) pairs per expert on, on average, the tcgen05 product runs
 
@@ -985,7 +1021,11 @@ def routed_experts(out: torch.Tensor, x: torch.Tensor, router: torch.Tensor, cor
   dt, st = _dt(x), _stream()
   Z = router.shape[0]
   logits = workspace.buffer("moe_logits", (T, Z), torch.float32)
-  linear(logits, x, router)
+  if x.dtype == torch.bfloat16 and T > SKINNY_BEST_M and Z <= ROUTER_KERNEL_MAX_COLUMNS and H % 8 == 0 and x.is_contiguous() and router.is_contiguous():
+    # many rows times a handful of columns: a library product would pad the columns to a tile
+    _check(lib, lib.mi_moe_router_logits(_ptr(logits, torch.float32), _ptr(x), _ptr(router), T, Z, H, st))
+  else:
+    linear(logits, x, router)
   _check(lib, lib.mi_moe_route(_ptr(logits, torch.float32), Z, T, _ptr(correction, torch.float32) if correction is not None else _ptr(None), E, top,
                                1 if weights == "softmax_chosen" else 0, _ptr(idx), _ptr(wts), st))
   shared_args = (_ptr(shared) if shared is not None else _ptr(None),
@@ -1077,8 +1117,9 @@ def glu_mul(out: torch.Tensor, gate_up: torch.Tensor, glu: str = "silu", limit: 
 
 def linear_glu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace, glu: str = "silu", limit: float = 0.0) -> None:
   """out[M, I] = act(x @ w[:I]^T) * (x @ w[I:]^T): the gate-and-up product of a gated feed-forward with the activation
-  ``glu``.  ``silu`` is ``linear_swiglu``; the others take the tcgen05 kernel with the activation in its epilogue from the
-  same number of rows on, and the product followed by the activation kernel below it."""
+  ``glu``.  ``silu`` is ``linear_swiglu``; the others take the few-row mma.sync kernel with the activation in its epilogue up to 16
+  rows, the tcgen05 kernel with the activation in its epilogue from the same number of rows on as SwiGLU, and the product
+  followed by the activation kernel between."""
   if glu == "silu":
     linear_swiglu(out, x, w, workspace)
     return
@@ -1089,6 +1130,11 @@ def linear_glu(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, workspace, g
   if M == 0:
     return
   kind, lim = _glu(glu, limit)
+  if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= SKINNY_BEST_M and K % 8 == 0 and x.is_contiguous() and w.is_contiguous()
+      and out.is_contiguous()):
+    lib = common_lib()      # few rows: the weight-streaming product with the activation in its epilogue
+    _check(lib, lib.mi_gemm_skinny_glu_bf16(_ptr(out), _ptr(x), _ptr(w), M, I, K, I, kind, lim, _stream()))
+    return
   many = M >= (GEMM_TC_MIN_M if K >= 4096 else GEMM_TC_MIN_M_NARROW)
   if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and many and K >= 64 and K % 8 == 0 and I % 8 == 0
       and x.is_contiguous() and w.is_contiguous() and out.is_contiguous() and os.environ.get("MINIINFER_B200_GEMM_TC", "1") != "0"):

@@ -230,9 +230,6 @@ class RglruMixer(Mixer):
     for k in ("ra_b", "ri_b"):      # one bias a channel, the parts one after the other
       if k in params:
         setattr(self, k, params[k].reshape(-1))
-    if "gates" in params:           # a part's stacked gate matrices, for the products a part
-      P = self.part
-      self.gate_parts = [params["gates"][2 * P * b:2 * P * (b + 1)] for b in range(self.blocks)]
 
   def validate(self, dtype: torch.dtype) -> None:
     if self.taps > 16:
@@ -250,15 +247,14 @@ class RglruMixer(Mixer):
     u = ctx.ws.buffer("rglru_u", (T, C), ctx.dtype)
     ops.causal_conv(u, proj[:, :C], self.conv, self.conv_b, state[:, :max(self.conv_floats, 1)], ctx, silu=False, in_bias=self.x_b)
     if T > ops.SKINNY_BEST_M and ctx.dtype == torch.bfloat16 and P % 8 == 0:
-      # many rows: a library product a part, on the tensor cores, each leaving its part's logits side by side
+      # many rows: the parts' products on the tensor cores, each leaving its part's logits side by side
       gates = ctx.ws.buffer("rglru_gates", (B, T, 2 * P), torch.float32)
-      for b in range(B):
-        ops.linear(gates[b], u[:, b * P:(b + 1) * P], self.gate_parts[b])
+      ops.linear_parts(gates, u, self.gates.view(B, 2 * P, P))
     else:
       gates = ctx.ws.buffer("rglru_gates", (T, 2 * C), torch.float32)
       ops.linear_batched(gates.view(T, B, 2 * P), u.view(T, B, P), self.gates.view(B, 2 * P, P))
     s = ctx.ws.buffer("rglru_s", (T, C), ctx.dtype)
-    ops.rglru_recurrence(s, u, gates, proj[:, C:], self.ra_b, self.ri_b, self.y_b, self.lam, state[:, self.conv_floats:], ctx, B)
+    ops.rglru_recurrence(s, u, gates, proj[:, C:], self.ra_b, self.ri_b, self.y_b, self.lam, state[:, self.conv_floats:], ctx, B, workspace=ctx.ws)
     out = ctx.ws.buffer(self.out_buffer, (T, self.hidden_size), ctx.dtype)
     ops.linear(out, s, self.w_o)
     return out
@@ -307,7 +303,7 @@ class MinGruMixer(Mixer):
     proj = ctx.ws.buffer("mingru_proj", (T, 3 * C), ctx.dtype)
     ops.linear(proj, x, self.w_in)
     s = ctx.ws.buffer("mingru_s", (T, C), ctx.dtype)
-    ops.mingru_recurrence(s, proj, self.z_b, self.x_b, state, ctx)
+    ops.mingru_recurrence(s, proj, self.z_b, self.x_b, state, ctx, workspace=ctx.ws)
     out = ctx.ws.buffer(self.out_buffer, (T, self.hidden_size), ctx.dtype)
     ops.linear(out, s, self.w_o)
     return out

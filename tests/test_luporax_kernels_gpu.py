@@ -133,20 +133,22 @@ def test_long_portions_in_stretches_side_by_side_agree_with_the_walk_in_order(C,
   proj = (torch.randn((T, 3 * C), generator=g) * 2.0).to(torch.bfloat16).to(DEV)
   proj[:, :C // 2] -= 5.0
   zb, xb = (torch.randn(C, generator=g) * 0.5).to(DEV), (torch.randn(C, generator=g) * 0.5).to(DEV)
+  from miniinfer_b200.engine.context import Workspace
   outs, states = [], []
-  for segments in ("1", "0"):
+  for segments, ws in (("1", Workspace(torch.device(DEV))), ("0", None), ("1", None)):      # prepared and walked, in order, walked as it is made
     monkeypatch.setenv("MINIINFER_B200_RECURRENCE_SEGMENTS", segments)
     state = torch.zeros((4, C), dtype=torch.float32, device=DEV)
     state[3] = torch.linspace(-1, 1, C)
     out = torch.zeros((T, C), dtype=torch.bfloat16, device=DEV)
     ctx = step_ctx([(800, 0, 2), (3, 0, 0), (800, 50, 3)])
     assert ops._recurrence_segmented(torch.bfloat16, ctx) == int(segments)
-    ops.mingru_recurrence(out, proj, zb, xb, state, ctx)
+    ops.mingru_recurrence(out, proj, zb, xb, state, ctx, workspace=ws)
     outs.append(out.float().cpu())
     states.append(state.cpu())
-  assert float((outs[0] - outs[1]).abs().max()) <= 2e-2 * float(outs[1].abs().max())
-  assert float((states[0] - states[1]).abs().max()) <= 1e-4 * float(states[1].abs().max())
-  assert torch.equal(outs[0][800:803], outs[1][800:803])
+  for k in (0, 2):
+    assert float((outs[k] - outs[1]).abs().max()) <= 2e-2 * float(outs[1].abs().max())
+    assert float((states[k] - states[1]).abs().max()) <= 1e-4 * float(states[1].abs().max())
+  assert torch.equal(outs[2][800:803], outs[1][800:803])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -331,3 +333,16 @@ def test_clamped_experts_with_a_gated_shared_expert(dtype, T, E, top, H, F, S):
   diff = (out.float().cpu() - want).abs().max(-1).values
   assert int(clear.sum()) >= 0.8 * T
   assert float(diff[clear].max()) <= (3e-5 if dtype == "float32" else 4e-2) * float(want.abs().max())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,parts,K,N", [(1, 3, 16, 32), (9, 1, 8, 16), (40, 5, 24, 48), (300, 2, 64, 128)])
+def test_a_block_diagonal_map_part_by_part(dtype, M, parts, K, N):
+  """out[b] = x[:, part b] @ w[b]^T: few rows (the batched kernels) and many (one strided batched library product)."""
+  from miniinfer_b200.kernels import ops
+  g = torch.Generator().manual_seed(M + parts)
+  x, w = rounded(torch.randn((M, parts * K), generator=g), dtype), rounded(torch.randn((parts, N, K), generator=g), dtype)
+  want = torch.einsum("mbk,bnk->bmn", x.double().view(M, parts, K), w.double()).float()
+  out = torch.zeros((parts, M, N), dtype=torch.float32, device=DEV)
+  ops.linear_parts(out, x.to(DT[dtype]).to(DEV), w.to(DT[dtype]).to(DEV))
+  assert float((out.cpu() - want).abs().max()) <= 2e-5 * float(want.abs().max())

@@ -231,7 +231,7 @@ def norm_scaled_add(resid, y, weight, eps, mult, ctx, copy=None, keep=None):
     copy.copy_(resid.to(copy.dtype))
 
 
-def rglru_recurrence(out, u, gates, y, r_bias, i_bias, y_bias, lam, state, ctx, blocks):
+def rglru_recurrence(out, u, gates, y, r_bias, i_bias, y_bias, lam, state, ctx, blocks, workspace=None):
   T, C = u.shape
   P = C // blocks
   g = gates.transpose(0, 1) if gates.dim() == 3 else gates.view(T, blocks, 2 * P)
@@ -245,7 +245,7 @@ def rglru_recurrence(out, u, gates, y, r_bias, i_bias, y_bias, lam, state, ctx, 
   _diagonal(out, a, b, gate, state, ctx, C)
 
 
-def mingru_recurrence(out, proj, z_bias, x_bias, state, ctx):
+def mingru_recurrence(out, proj, z_bias, x_bias, state, ctx, workspace=None):
   C = out.shape[1]
   zl = proj[:, :C].float() + (z_bias if z_bias is not None else 0.0)
   x = proj[:, C:2 * C].float() + (x_bias if x_bias is not None else 0.0)
@@ -360,6 +360,11 @@ def linear_batched(out, x, w, bias=None, softplus=False, row_gate=None):
   if row_gate is not None:
     y = y * torch.sigmoid(row_gate.float()[:, :x.shape[1], None])
   out.copy_(y.to(out.dtype))
+
+
+def linear_parts(out, x, w):
+  B, N, K = w.shape
+  out.copy_(torch.einsum("mbk,bnk->bmn", x.float().view(x.shape[0], B, K), w.float()).to(out.dtype))
 
 
 def _items(ctx):
@@ -568,5 +573,5 @@ def install(monkeypatch) -> None:
                "attention", "routed_experts", "silu_mul", "sample", "linear_normed", "linear_swiglu_normed", "linear_add",
                "add_rmsnorm_pair", "rms_pair_sum", "linear_batched", "causal_conv", "selective_scan", "gated_delta", "latent_down",
                "latent_query", "linear_attention", "hyper_connection", "relu_squared", "linear_relu_squared", "scaled_pair_sum",
-               "glu_mul", "linear_glu", "token_shift", "norm_scaled_add", "rglru_recurrence", "mingru_recurrence"):
+               "glu_mul", "linear_glu", "linear_parts", "token_shift", "norm_scaled_add", "rglru_recurrence", "mingru_recurrence"):
     monkeypatch.setattr(ops, name, globals()[name])
