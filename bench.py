@@ -408,8 +408,9 @@ def kernel_case(name: str, reps: int = 3) -> str:
   rnd = lambda *shape, dtype=torch.bfloat16, scale=1.0: (torch.randn(*shape, generator=g, device=dev) * scale).to(dtype)
   ws = Workspace(dev)
 
-  def attention_case(dtype, page, items):
-    """items: (context length, new tokens) per request; the cache holds random keys and values."""
+  def attention_case(dtype, page, items, **shaped):
+    """items: (context length, new tokens) per request; the cache holds random keys and values.  ``shaped``: a cap on the
+    scores, sigmoid weights."""
     nh, nkv, hd = 16, 8, 128
     pages_per = [-(-c // page) for c, _ in items]
     kv = rnd(sum(pages_per) + 1, 2, nkv, page, hd, dtype=dtype)
@@ -437,7 +438,10 @@ def kernel_case(name: str, reps: int = 3) -> str:
                            num_decode=len(dec), max_ctx_len=max(c for c, _ in items), scratch=ws)
     qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=dtype)
     out = torch.empty(T, nh * hd, dtype=dtype, device=dev)
-    return lambda: ops.attention(out, qkv, kv, bt.to(dev), batch, nh, nkv, hd, hd ** -0.5, None), f"{len(items)} requests {items[:2]}.., page {page}, {dtype}"
+    if shaped.get("sigmoid"):
+      shaped = {"softcap": shaped.get("softcap", 0.0), "score_bias": torch.full((nh,), -2.0, device=dev)}
+    return (lambda: ops.attention(out, qkv, kv, bt.to(dev), batch, nh, nkv, hd, hd ** -0.5, None, **shaped),
+            f"{len(items)} requests {items[:2]}.., page {page}, {dtype}" + (", capped scores, sigmoid weights" if shaped else ""))
 
   if name == "sample":
     R, V = 256, 151936
@@ -468,6 +472,10 @@ def kernel_case(name: str, reps: int = 3) -> str:
     fn, what = attention_case(torch.bfloat16, 64, [(2048, 2048)])           # the tcgen05 kernel, blocks alone
   elif name == "attention_prefill_tc_pairs":
     fn, what = attention_case(torch.bfloat16, 64, [(8192, 8192)])           # enough tiles of 128 tokens for blocks in pairs
+  elif name == "attention_prefill_tc_sigmoid":
+    fn, what = attention_case(torch.bfloat16, 64, [(2048, 2048)], softcap=50.0, sigmoid=True)       # the tcgen05 kernel on shaped scores
+  elif name == "attention_decode_tma_sigmoid":
+    fn, what = attention_case(torch.bfloat16, 64, [(2048 + 8 * i, 1) for i in range(64)], softcap=50.0, sigmoid=True)
   elif name == "attention_prefill_mma":
     fn, what = attention_case(torch.bfloat16, 16, [(2048, 2048)])           # pages of 16 tokens: not the tcgen05 kernel's
   elif name == "attention_decode_cpasync":
@@ -525,6 +533,26 @@ def kernel_case(name: str, reps: int = 3) -> str:
     fn = lambda: ops.linear_attention(out, q, k, v, gate, state, ctx, H, Dk, Dv, 1e-6, decay_logits=logits, decay_bias=bias, tau=16.0,
                                       q_scale=Dk ** -0.5, norm_weight=norm_w, workspace=ws)
     what = f"{T} tokens ({cuts[0]} of one request), {H} heads of {Dk} x {Dv}, decays per channel"
+  elif name in ("rglru_recurrence", "mingru_recurrence"):
+    # one prompt portion of 8192 tokens (prepared by a kernel of its own, walked in 32 stretches a block) beside seven decode
+    # tokens of other requests, 4096 channels (MINIINFER_B200_RECURRENCE_SEGMENTS=0 in the environment: the walk in order)
+    from types import SimpleNamespace
+    cuts = [8192] + [1] * 7
+    T, C, B = sum(cuts), 4096, 8
+    it = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    ctx = SimpleNamespace(q_start=it([sum(cuts[:i]) for i in range(len(cuts))]), q_len=it(cuts), seq_slot=it(list(range(len(cuts)))),
+                          num_items=len(cuts), num_tokens=T, token_item=it([b for b, n in enumerate(cuts) for _ in range(n)]))
+    state = torch.zeros((len(cuts), C), dtype=torch.float32, device=dev)
+    out = torch.empty(T, C, dtype=torch.bfloat16, device=dev)
+    if name == "rglru_recurrence":
+      u, y, gates = rnd(T, C), rnd(T, C), rnd(T, 2 * C, dtype=torch.float32)
+      rb, ib, yb, lam = (rnd(C, dtype=torch.float32) for _ in range(4))
+      fn = lambda: ops.rglru_recurrence(out, u, gates, y, rb, ib, yb, lam - 3.0, state, ctx, B, workspace=ws)
+      what = f"{T} tokens ({cuts[0]} of one request), {C} channels in {B} parts ({T * C * 14 / 1e6:.0f} MB of activations in and out)"
+    else:
+      proj, zb, xb = rnd(T, 3 * C), rnd(C, dtype=torch.float32), rnd(C, dtype=torch.float32)
+      fn = lambda: ops.mingru_recurrence(out, proj, zb, xb, state, ctx, workspace=ws)
+      what = f"{T} tokens ({cuts[0]} of one request), {C} channels ({T * C * 8 / 1e6:.0f} MB of activations in and out)"
   elif name == "hyper_connection":
     # the kernel between two sublayers: 16384 rows of 4 streams x 2048 values float32 (537 MB, read and written) and a bfloat16 sublayer output
     T, S, W = 16384, 4, 2048
@@ -549,7 +577,8 @@ def kernel_case(name: str, reps: int = 3) -> str:
 
 KERNEL_CASES = ("sample", "silu_mul", "gemm_f32", "gemm_tc_plain", "gemm_stream", "attention_generic", "attention_prefill_tc",
                 "attention_prefill_tc_pairs", "attention_prefill_mma", "attention_decode_cpasync", "experts_many_rows", "experts_few_rows",
-                "selective_scan", "delta_rule", "linear_attention", "hyper_connection")
+                "selective_scan", "delta_rule", "linear_attention", "hyper_connection", "attention_prefill_tc_sigmoid", "attention_decode_tma_sigmoid",
+                "rglru_recurrence", "mingru_recurrence")
 
 
 def mixed_workload(model_dir: str, requests: int = 64, outputs: int = 256) -> dict:

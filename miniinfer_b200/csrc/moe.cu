@@ -141,49 +141,6 @@ moe_align_atomic_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, in
   }
 }
 
-// The router's logits for many rows in bfloat16: z[t, e] = x[t] . router[e], float32 sums of exact products.  A product of
-// very few columns (the experts) for which a library picks a tile of 64 columns and wastes most of it; here a warp takes a
-// token, reads its row once (16 bytes a lane and step) and keeps up to 16 sums at a time, the router's rows coming from L1.
-constexpr int RL_WARPS = 8, RL_E = 16;
-__global__ void __launch_bounds__(RL_WARPS * 32)
-moe_router_logits_kernel(float* __restrict__ z, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ router, int Tn, int Z, int H) {
-  mi::grid_dependency_sync();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t = blockIdx.x * RL_WARPS + warp;
-  if (t >= Tn) return;
-  const __nv_bfloat16* xr = x + (size_t)t * H;
-  for (int e0 = 0; e0 < Z; e0 += RL_E) {
-    float acc[RL_E];
-#pragma unroll
-    for (int e = 0; e < RL_E; ++e) acc[e] = 0.f;
-    for (int k = lane * 8; k < H; k += 256) {
-      const uint4 xv = *reinterpret_cast<const uint4*>(xr + k);
-      const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
-      float xf[8];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(xp[i]); xf[2 * i] = f.x; xf[2 * i + 1] = f.y; }
-#pragma unroll
-      for (int e = 0; e < RL_E; ++e) {
-        if (e0 + e < Z) {
-          const uint4 wv = *reinterpret_cast<const uint4*>(router + (size_t)(e0 + e) * H + k);
-          const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 f = __bfloat1622float2(wp[i]);
-            acc[e] = fmaf(xf[2 * i], f.x, acc[e]);
-            acc[e] = fmaf(xf[2 * i + 1], f.y, acc[e]);
-          }
-        }
-      }
-    }
-#pragma unroll
-    for (int e = 0; e < RL_E; ++e) {
-      const float s = mi::warp_sum(acc[e]);
-      if (lane == 0 && e0 + e < Z) z[(size_t)t * Z + e0 + e] = s;
-    }
-  }
-}
-
 // ---------------------------------------------------------------------------------------------- products
 
 struct GroupedArgs {
@@ -549,17 +506,6 @@ int launch_bf16(const GroupedArgs& a, int tiles, cudaStream_t stream) {
 MI_API int mi_moe_row_tile(int n_pairs, int E, int dtype) {
   if (dtype == MI_F32) return FTM;
   return n_pairs >= 32 * E ? 64 : 16;
-}
-
-// z[T, Z] = x[T, H] router[Z, H]^T in float32 from bfloat16 rows, for the few columns of a router (H a multiple of 8, 16-byte aligned rows).
-MI_API int mi_moe_router_logits(float* z, const void* x, const void* router, int T, int Z, int H, cudaStream_t stream) {
-  MI_REQUIRE(T >= 0 && Z > 0 && H > 0 && H % 8 == 0, "moe_router_logits: rows of %d values (a multiple of 8 in bfloat16)", H);
-  MI_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)router % 16) == 0, "moe_router_logits: operands must be 16-byte aligned");
-  if (T == 0) return 0;
-  mi::launch(moe_router_logits_kernel, dim3((T + RL_WARPS - 1) / RL_WARPS), dim3(RL_WARPS * 32), 0, stream, z, (const __nv_bfloat16*)x,
-             (const __nv_bfloat16*)router, T, Z, H);
-  MI_LAUNCH_OK("moe_router_logits");
-  return 0;
 }
 
 // z: the router's logits in float32, rows of z_stride >= E values (a product of the engine's own: W_router h with float32

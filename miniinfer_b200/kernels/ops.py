@@ -944,7 +944,6 @@ def latent_query(q: torch.Tensor, q_out: torch.Tensor, heads: int, dim: int, rot
                                   _ptr(positions, torch.int32), int(bool(interleaved)), _stream()))
 
 
-ROUTER_KERNEL_MAX_COLUMNS = 64   # up to this many router rows the logits of many tokens come from a kernel of this package
 MOE_TC_ROW_TILE = 256            # rows of a stretch of the tcgen05 grouped product: what a pair of blocks takes at a time
 MOE_TC_MIN_ROWS_PER_EXPERT = 128   # from this many (token, choice) pairs per expert on, on average, the tcgen05 product runs
 
@@ -1021,11 +1020,7 @@ def routed_experts(out: torch.Tensor, x: torch.Tensor, router: torch.Tensor, cor
   dt, st = _dt(x), _stream()
   Z = router.shape[0]
   logits = workspace.buffer("moe_logits", (T, Z), torch.float32)
-  if x.dtype == torch.bfloat16 and T > SKINNY_BEST_M and Z <= ROUTER_KERNEL_MAX_COLUMNS and H % 8 == 0 and x.is_contiguous() and router.is_contiguous():
-    # many rows times a handful of columns: a library product would pad the columns to a tile
-    _check(lib, lib.mi_moe_router_logits(_ptr(logits, torch.float32), _ptr(x), _ptr(router), T, Z, H, st))
-  else:
-    linear(logits, x, router)
+  linear(logits, x, router)
   _check(lib, lib.mi_moe_route(_ptr(logits, torch.float32), Z, T, _ptr(correction, torch.float32) if correction is not None else _ptr(None), E, top,
                                1 if weights == "softmax_chosen" else 0, _ptr(idx), _ptr(wts), st))
   shared_args = (_ptr(shared) if shared is not None else _ptr(None),
