@@ -108,8 +108,11 @@ class ClockSampler:
       for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[2:]):
         if v.lower().startswith("active"):
           reasons.add(name)
-    mhz.sort()
-    return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(mhz)}
+    # the median under load: a run that builds models between its timed stretches leaves the GPU idle (at a few hundred
+    # MHz) for most of its samples; those that lie below a third of the maximum are idle ones and do not count
+    busy = sorted(m for m in mhz if mx and m >= mx / 3.0) or sorted(mhz)
+    return {"sm_mhz": busy[len(busy) // 2] if busy else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(mhz),
+            "samples_under_load": len(busy)}
 
 
 def model_bytes(cfg: dict, layers: int) -> dict:
