@@ -781,7 +781,7 @@ def _compare_groups(times: dict) -> dict:
   for name, us in times.items():
     if re.search(r"decode_tma_kernel|decode_cluster_kernel|decode_split_kernel|decode_merge|attention_prefill|attention_generic", name):
       g["attention"] += us
-    elif "moe_gemm" in name or "moe_stream" in name or re.search(r"gemm_tc_kernel<\w+, \w+, (true|\(bool\)1)>", name):     # the grouped instantiation of the tcgen05 product
+    elif "moe_gemm" in name or "moe_stream" in name or re.search(r"gemm_tc_kernel<\w+, \w+, (true|\(bool\)1)[,>]", name):     # the grouped instantiation of the tcgen05 product
       g["experts"] += us
     elif re.search(r"moe_route|moe_align|moe_combine", name):
       g["routing"] += us
@@ -1258,7 +1258,7 @@ def _luporax_groups(times: dict) -> dict:
   for name, us in times.items():
     if re.search(r"decode_tma_kernel|decode_cluster_kernel|decode_split_kernel|decode_merge|attention_prefill|attention_generic", name):
       g["attention"] += us
-    elif "moe_gemm" in name or "moe_stream" in name or re.search(r"gemm_tc_kernel<\w+, \w+, (true|\(bool\)1)>", name):
+    elif "moe_gemm" in name or "moe_stream" in name or re.search(r"gemm_tc_kernel<\w+, \w+, (true|\(bool\)1)[,>]", name):
       g["experts"] += us
     elif re.search(r"moe_route|moe_align|moe_combine|moe_gather", name):
       g["routing"] += us

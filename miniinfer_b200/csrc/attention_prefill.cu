@@ -113,6 +113,8 @@ __device__ __forceinline__ void load_kv_block(__nv_bfloat16* ks, __nv_bfloat16* 
   }
 }
 
+// SHAPED: the form for shaped scores, compiled apart so that the plain softmax carries none of it.
+template <bool SHAPED>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_prefill_kernel(PrefillArgs a) {
   mi::grid_dependency_sync();
@@ -160,7 +162,7 @@ attention_prefill_kernel(PrefillArgs a) {
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int pr[2] = {p0 + warp * 16 + g, p0 + warp * 16 + g + 8};    // positions of this thread's two rows
   const bool row_ok[2] = {warp * 16 + g < rows, warp * 16 + g + 8 < rows};
-  const bool shaped = a.softcap > 0.f || a.score_bias != nullptr, sigmoid = a.score_bias != nullptr;
+  const bool shaped = SHAPED, sigmoid = SHAPED && a.score_bias != nullptr;
   const float head_bias = sigmoid ? a.score_bias[head] : 0.f;
 
   // ldmatrix lane addressing: lane l gives the row address of 8x8 matrix l/8, row l%8
@@ -339,11 +341,13 @@ MI_API int mi_attention_prefill_bf16(void* out, const void* q_base, int q_stride
   const size_t smem = (size_t)(BQ + 4 * BK) * LDS * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return mi_fail("attention_prefill: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  mi::launch(attention_prefill_kernel, dim3(dim3(n_tiles, nh)), dim3(WARPS * 32), smem, stream, a);
+  if (softcap > 0.f || score_bias != nullptr) mi::launch(attention_prefill_kernel<true>, dim3(dim3(n_tiles, nh)), dim3(WARPS * 32), smem, stream, a);
+  else mi::launch(attention_prefill_kernel<false>, dim3(dim3(n_tiles, nh)), dim3(WARPS * 32), smem, stream, a);
   MI_LAUNCH_OK("attention_prefill");
   return 0;
 }

@@ -172,8 +172,9 @@ struct Args {
   const __nv_bfloat16* gate;     // [T, gate_stride] or null: the output is multiplied with sigmoid(gate[token, head * HD + d])
   int gate_stride;
   // shaped scores (attention_scores.cuh): a cap on the scaled scores (0: none), and sigmoid weights with a bias per query
-  // head that are not normalised over the keys (null: softmax).  A shaped score enters the softmax as the base-2 logarithm
-  // of its weight, and the output is multiplied with 2^m at the end where the softmax divides by the sum.
+  // head that are not normalised over the keys (null: softmax).  A capped score enters the softmax as its base-2 logit.
+  // Sigmoid weights are written to P as they are - they lie in (0, 1), so there is no maximum to keep and no row of the
+  // output to rescale - and the output rows are stored as the products leave them.
   float scale, softcap;
   const float* score_bias;
 };
@@ -443,7 +444,10 @@ __device__ __forceinline__ int nth_work(int i, int b, int blocks, int total) {
   return w < total ? w : -1;
 }
 
-template <int CTAS>
+// SCORES: 0 - the softmax of the scaled scores; 1 - of capped scores; 2 - sigmoid weights (capped or not).  The forms for
+// shaped scores are compiled apart: as branches on values of Args in the one kernel they cost the plain softmax a quarter of
+// its speed.
+template <int CTAS, int SCORES = 0>
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, Args a) {
   using R = Ring<CTAS>;
@@ -658,7 +662,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     const int q = warp & 3, st = warp >> 2;
     const int r = q * 32 + lane;                           // row of the block = lane of the tensor memory
     const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
-    const bool shaped = a.softcap > 0.f || a.score_bias != nullptr, sigmoid = a.score_bias != nullptr;
+    constexpr bool shaped = SCORES != 0, sigmoid = SCORES == 2;
     const float sc = shaped ? 1.f : a.scale_log2;          // shaped scores come as base-2 logits already
     int o_seen = 0;
     auto wait_o = [&](int upto) {
@@ -702,9 +706,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_issuer<CTAS>(s_free);
-        if (shaped) {
+        if (sigmoid) {
 #pragma unroll
-          for (int e = 0; e < BN; ++e) v[e] = mi::shaped_logit2(v[e], a.scale, a.softcap, sigmoid, head_bias);
+          for (int e = 0; e < BN; ++e) v[e] = mi::shaped_sigmoid_weight(v[e], a.scale, a.softcap, head_bias);
+        } else if (shaped) {
+#pragma unroll
+          for (int e = 0; e < BN; ++e) v[e] = mi::shaped_logit2(v[e], a.scale, a.softcap, false, 0.f);
         }
         if (masked) {
           // A tile that the mask touches: the scores a row may not see are set to -inf once, here, and everything
@@ -715,10 +722,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
           const unsigned span = (unsigned)(last - first);
           // kept first keys are a second stretch, 0 .. kept - 1 (as far as the row has come), ahead of the window's
           const int kept = (a.window > 0 ? min(a.keep_first, pos + 1) : 0) - key0;
+          const float hidden = sigmoid ? 0.f : -INFINITY;      // a weight of nothing, or a score whose exponential is nothing
 #pragma unroll
-          for (int e = 0; e < BN; ++e) v[e] = ((unsigned)(e - first) <= span || e < kept) ? v[e] : -INFINITY;
+          for (int e = 0; e < BN; ++e) v[e] = ((unsigned)(e - first) <= span || e < kept) ? v[e] : hidden;
         }
-        {
+        if (sigmoid) {
+          // the weights as they are: P in bfloat16, two keys to a column; no maximum, no sum, no rescaling
+          m_run = 0.f;
+#pragma unroll
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) packed[e] = pack_bf16(v[32 * c + 2 * e], v[32 * c + 2 * e + 1]);
+            if (c == 0 && kk > 0) wait_o(kk - 1);          // the product that read the stream's P before has run
+            tmem_st16(p_addr + 16 * c, packed);
+          }
+        } else {
           float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
           for (int e = 0; e < BN; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], v[e]);
@@ -788,9 +807,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       const float l_all = fl[r] * w0 + fl[BM + r] * w1 + (a.sink ? exp2f(sink2 - m_all) : 0.f);
       constexpr int OD = HD / 2;                           // output columns of this thread
       const bool has1 = n > 1;
-      // sigmoid weights: a stream's row holds weight * 2^(-m) summed over its keys; nothing is divided by the weights' sum
-      const float f0 = sigmoid ? (m0 == -INFINITY ? 0.f : exp2f(m0)) : w0 / l_all;
-      const float f1 = has1 ? (sigmoid ? (m1 == -INFINITY ? 0.f : exp2f(m1)) : w1 / l_all) : 0.f;
+      // sigmoid weights: a stream's row holds the plain sum of the weighted values; nothing is divided by the weights' sum
+      const float f0 = sigmoid ? 1.f : w0 / l_all;
+      const float f1 = has1 ? (sigmoid ? 1.f : w1 / l_all) : 0.f;
       (void)head; (void)row_valid;
       float o0[OD], o1[OD];
       if (has1) {
@@ -889,9 +908,9 @@ namespace {
 
 // Launches the kernel for blocks that work alone (CTAS = 1) or in pairs (2).  `placed` tells whether pairs can be
 // resident on this device at all; if not, nothing was launched and the caller takes the other form.
-template <int CTAS>
+template <int CTAS, int SCORES = 0>
 int launch_prefill_tc(const CUtensorMap& qm, const CUtensorMap& km, const Args& a, int num_sms, cudaStream_t stream, bool* placed) {
-  auto kernel = attention_prefill_tc_kernel<CTAS>;
+  auto kernel = attention_prefill_tc_kernel<CTAS, SCORES>;
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
@@ -982,6 +1001,7 @@ MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_
   memcpy(&qm, q_map, sizeof(qm));
   memcpy(&km, kv_map, sizeof(km));
   const bool even_group = (nh / nkv) % 2 == 0;
+  const int scores = score_bias != nullptr ? 2 : (softcap > 0.f ? 1 : 0);
   bool placed = false;
   if (pairs && HD == 128 && even_group && num_sms >= 2 && tiles128 != nullptr && n_tiles128 > 0) {
     // a pair of blocks: 128 tokens of two neighbouring heads, a head each
@@ -991,7 +1011,8 @@ MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_
     p.hpt = 1;
     p.hw = 2;
     p.skip_odd = 0;
-    const int r = launch_prefill_tc<2>(qm, km, p, num_sms, stream, &placed);
+    const int r = scores == 2 ? launch_prefill_tc<2, 2>(qm, km, p, num_sms, stream, &placed)
+                : scores == 1 ? launch_prefill_tc<2, 1>(qm, km, p, num_sms, stream, &placed) : launch_prefill_tc<2>(qm, km, p, num_sms, stream, &placed);
     if (r != 0) return r;
   }
   if (!placed) {
@@ -1003,7 +1024,8 @@ MI_API int mi_attention_prefill_tc(void* out, const void* q_map, const void* kv_
       a.n_tiles = n_tiles128;
       a.skip_odd = 0;
     }
-    const int r = launch_prefill_tc<1>(qm, km, a, num_sms, stream, &placed);
+    const int r = scores == 2 ? launch_prefill_tc<1, 2>(qm, km, a, num_sms, stream, &placed)
+                : scores == 1 ? launch_prefill_tc<1, 1>(qm, km, a, num_sms, stream, &placed) : launch_prefill_tc<1>(qm, km, a, num_sms, stream, &placed);
     if (r != 0) return r;
   }
   MI_LAUNCH_OK("attention_prefill_tc");

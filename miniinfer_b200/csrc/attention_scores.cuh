@@ -44,4 +44,16 @@ __device__ __forceinline__ float shaped_logit2(float raw, float scale, float sof
   return -lg2_fast(1.f + ex2_fast(-(x + head_bias) * LOG2E));
 }
 
+// The weight itself, sigmoid(cap(scale * raw) + head_bias), for kernels that keep sigmoid weights as they are: they lie in
+// (0, 1), so nothing has to be held against a running maximum.
+__device__ __forceinline__ float shaped_sigmoid_weight(float raw, float scale, float softcap, float head_bias) {
+  constexpr float LOG2E = 1.4426950408889634f;
+  float x = raw * scale;
+  if (softcap > 0.f) {
+    const float e = ex2_fast(fminf(x * (2.f * LOG2E / softcap), 60.f));
+    x = softcap * (1.f - __fdividef(2.f, 1.f + e));
+  }
+  return __fdividef(1.f, 1.f + ex2_fast(fminf(-(x + head_bias) * LOG2E, 80.f)));      // beyond 2^80 the weight is nothing
+}
+
 }  // namespace mi

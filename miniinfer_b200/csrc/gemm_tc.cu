@@ -77,8 +77,7 @@ struct Args {
   const int* tile_expert;
   int tile_rows, expert_rows;
   int act;               // plain product only: 1 - out = max(bf16(product), 0)^2, the squared ReLU of a feed-forward; 0 - the product
-  int glu;               // gate-and-up product only: the gated activation (a MiGlu of common.cuh) and its limit
-  float limit;
+  float limit;           // gate-and-up product only: the limit of a clamped gated activation (the template's GLU)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -218,7 +217,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <bool SWIGLU, int CTAS, bool GROUPED>
+// GLU (gate-and-up products): the gated activation of the epilogue, a MiGlu of common.cuh, known when the kernel is compiled -
+// as a value of Args it cost the SwiGLU epilogue a fifth of its speed.
+template <bool SWIGLU, int CTAS, bool GROUPED, int GLU = MI_GLU_SILU>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map, Args a) {
   using S = Shape<CTAS>;
@@ -372,7 +373,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const float gg = round_bf16(g[i]), uu = round_bf16(u[i]);
-            g[i] = mi::glu_fast(gg, uu, a.glu, a.limit);
+            g[i] = GLU == MI_GLU_SILU ? mi::silu_mul_fast(gg, uu) : mi::glu_fast(gg, uu, GLU, a.limit);
           }
         } else if (a.act == 1) {
           // the values the product followed by the activation kernel leaves: rounded, clamped, squared
@@ -441,10 +442,10 @@ int encode_map(CUtensorMap* map, const void* base, long long rows, long long col
   return 0;
 }
 
-template <bool SWIGLU, int CTAS, bool GROUPED>
+template <bool SWIGLU, int CTAS, bool GROUPED, int GLU = MI_GLU_SILU>
 int launch_tc(const CUtensorMap& xm, const CUtensorMap& wm, const Args& a, int sms, cudaStream_t stream, bool* placed) {
   using S = Shape<CTAS>;
-  auto kernel = gemm_tc_kernel<SWIGLU, CTAS, GROUPED>;
+  auto kernel = gemm_tc_kernel<SWIGLU, CTAS, GROUPED, GLU>;
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM_BYTES);
@@ -497,7 +498,7 @@ int launch_tc(const CUtensorMap& xm, const CUtensorMap& wm, const Args& a, int s
   return 0;
 }
 
-template <bool SWIGLU, bool GROUPED = false>
+template <bool SWIGLU, bool GROUPED = false, int GLU = MI_GLU_SILU>
 int run(void* out, const void* x, const void* w, int M, int N, int K, int ldo, int* status, int pairs, cudaStream_t stream,
         int experts = 1, const int* tile_expert = nullptr, int tile_rows = 0, int act = 0, int glu = MI_GLU_SILU, float limit = 0.f) {
   // N: output columns; w has N rows (plain) or 2 N rows (SwiGLU), per expert
@@ -511,7 +512,8 @@ int run(void* out, const void* x, const void* w, int M, int N, int K, int ldo, i
   a.tile_expert = tile_expert;
   a.tile_rows = tile_rows;
   a.act = SWIGLU ? 0 : act;
-  a.glu = glu; a.limit = limit;
+  a.limit = limit;
+  (void)glu;
   a.expert_rows = SWIGLU ? 2 * N : N;
   a.out = (__nv_bfloat16*)out;
   a.status = status;
@@ -526,10 +528,10 @@ int run(void* out, const void* x, const void* w, int M, int N, int K, int ldo, i
   if (sms < 2) pairs = 0;
   bool placed = false;
   if (pairs) {
-    if (int e = launch_tc<SWIGLU, 2, GROUPED>(xm, wm, a, sms, stream, &placed)) return e;
+    if (int e = launch_tc<SWIGLU, 2, GROUPED, GLU>(xm, wm, a, sms, stream, &placed)) return e;
   }
   if (!placed) {
-    if (int e = launch_tc<SWIGLU, 1, GROUPED>(xm, wm, a, sms > 0 ? sms : 1, stream, &placed)) return e;
+    if (int e = launch_tc<SWIGLU, 1, GROUPED, GLU>(xm, wm, a, sms > 0 ? sms : 1, stream, &placed)) return e;
   }
   return 0;
 }
@@ -547,7 +549,8 @@ MI_API int mi_gemm_tc_swiglu_bf16(void* out, const void* x, const void* w, int M
 MI_API int mi_gemm_tc_glu_bf16(void* out, const void* x, const void* w, int M, int I, int K, int ldo, int* status,
                                int pairs, int glu, float limit, cudaStream_t stream) {
   MI_REQUIRE(glu == MI_GLU_SILU || (glu == MI_GLU_CLAMPED && limit > 0.f), "gemm_tc_glu: unknown activation %d or a limit that is not positive", glu);
-  return run<true>(out, x, w, M, I, K, ldo, status, pairs, stream, 1, nullptr, 0, 0, glu, limit);
+  if (glu == MI_GLU_CLAMPED) return run<true, false, MI_GLU_CLAMPED>(out, x, w, M, I, K, ldo, status, pairs, stream, 1, nullptr, 0, 0, glu, limit);
+  return run<true>(out, x, w, M, I, K, ldo, status, pairs, stream);
 }
 
 // The grouped form: x [M, K] holds rows sorted by expert, every expert's rows starting at a multiple of tile_rows (a
@@ -559,7 +562,9 @@ MI_API int mi_gemm_tc_grouped_bf16(void* out, const void* x, const void* w, int 
   MI_REQUIRE(glu == MI_GLU_SILU || (glu == MI_GLU_CLAMPED && limit > 0.f), "gemm_tc_grouped: unknown activation %d or a limit that is not positive", glu);
   MI_REQUIRE(experts > 0 && tile_expert != nullptr && tile_rows > 0 && tile_rows % 256 == 0 && M % tile_rows == 0,
              "gemm_tc_grouped: rows=%d must come in stretches of tile_rows=%d, a multiple of 256", M, tile_rows);
-  return swiglu ? run<true, true>(out, x, w, M, N, K, ldo, status, pairs, stream, experts, tile_expert, tile_rows, 0, glu, limit)
+  if (swiglu && glu == MI_GLU_CLAMPED)
+    return run<true, true, MI_GLU_CLAMPED>(out, x, w, M, N, K, ldo, status, pairs, stream, experts, tile_expert, tile_rows, 0, glu, limit);
+  return swiglu ? run<true, true>(out, x, w, M, N, K, ldo, status, pairs, stream, experts, tile_expert, tile_rows)
                 : run<false, true>(out, x, w, M, N, K, ldo, status, pairs, stream, experts, tile_expert, tile_rows);
 }
 
