@@ -332,7 +332,10 @@ def _layer(kind, mixer, mlp, weights_of) -> dict:
 # 16, three parts in the recurrent unit, a layer without a feed-forward, layers that run another's weights (one of them
 # twice).  B: as many key/value heads as query heads, the whole head rotated, no cap on the scores, a recurrent unit of
 # one part whose convolution has one tap, a router that takes all of its experts and one that takes one, a feed-forward
-# without a shared expert, multipliers of 1.  C: heads of 64 (the tensor-core and tensor-copy kernels), pages of 64.
+# without a shared expert, multipliers of 1.  C: heads of 64 (the tensor-core and tensor-copy kernels), pages of 64.  D: odd
+# sizes - a width of 72, a vocabulary of 333, sixteen query heads on one key/value head, a cap of 5 that bites, a rotation
+# of 8 of 32 values, a convolution of 7 taps over 5 parts of 8 channels, 40 experts of which a token takes 6, a multiplier
+# above 1 and an eps of 1e-3.
 _A_MLP = moe(24, 1.5, 5, 2, (16, 0.8))
 _C_MLP = moe(64, 2.5, 8, 3, (96, 1.2))
 CONFIGS = {
@@ -352,4 +355,9 @@ CONFIGS = {
     rglru_layer(96, 2, 4, _C_MLP),
     mingru_layer(160, _C_MLP),
     attention(8, 2, 64, 64, 32, 20000.0, 0.125, 30.0, _C_MLP, weights_of=0)]},
+  "D": {"architecture": "Luporax", "vocab": 333, "width": 72, "norm": {"eps": 1e-3}, "residual_mult": 1.3, "logit_scale": 0.07, "layers": [
+    rglru_layer(40, 5, 7, moe(16, 0.5, 40, 6, (8, 3.0))),
+    attention(16, 1, 32, 48, 8, 3000.0, 0.9, 5.0, moe(16, 0.5, 40, 6, (8, 3.0))),
+    attention(16, 1, 32, 48, 8, 3000.0, 0.9, 5.0, moe(16, 0.5, 40, 6, (8, 3.0)), weights_of=1),
+    mingru_layer(24, None)]},
 }

@@ -126,7 +126,7 @@ def test_random_weights_mode_writes_a_model_of_the_design(tmp_path):
   assert float(W["l0.mix.ra"].abs().sum()) > 0 and torch.isfinite(plain.forward(cfg, W, [1, 2, 3])).all()
 
 
-@pytest.mark.parametrize("tag,page", [("A", 16), ("B", 8), ("C", 64)])
+@pytest.mark.parametrize("tag,page", [("A", 16), ("B", 8), ("C", 64), ("D", 16)])
 def test_every_cut_gives_the_plain_logits_on_the_host_path(cpu_kernels, tmp_path, tag, page):
   from miniinfer_b200.engine.replay import TraceRunner
   cfg = plain.CONFIGS[tag]

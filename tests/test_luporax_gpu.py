@@ -14,8 +14,9 @@ from gpu_helpers import DEV
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": (5, 17, 33, 100, 64, 128, 41, 65, 1, 2), "B": (1, 9, 40, 71, 130, 65, 200, 2), "C": (130, 70, 300, 64, 200, 65, 257)}
-PAGES = {"A": 16, "B": 16, "C": 64}
+LENGTHS = {"A": (5, 17, 33, 100, 64, 128, 41, 65, 1, 2), "B": (1, 9, 40, 71, 130, 65, 200, 2), "C": (130, 70, 300, 64, 200, 65, 257),
+           "D": (3, 50, 129, 70, 1, 16)}
+PAGES = {"A": 16, "B": 16, "C": 64, "D": 16}
 # bfloat16, as fractions of the root mean square of the plain logits: rounding every product to bfloat16 moves a row by a
 # few hundredths of that.  A router's close call, decided the other way after rounding, moves single rows by more (an
 # expert is exchanged for its neighbour), which is why one row in twenty may pass the bound; a lost state, a shift from a
@@ -72,7 +73,7 @@ def compare(got, ref, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("tag", ["A", "B", "C"])
+@pytest.mark.parametrize("tag", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed", "preempted"])
 def test_every_cut_gives_the_plain_logits(luporax_dirs, dtype, tag, cut):
   d = luporax_dirs(tag)
@@ -120,6 +121,27 @@ def test_long_decoding_over_page_borders(luporax_dirs, dtype, tag):
   got = {k: v for k, v in got.items() if k[0] == "r0" or k[1] < pos_b}
   compare(got, ref, dtype, f"luporax long decode {tag}/{dtype}")
   runner.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_prompts_whole_and_in_large_portions(luporax_dirs, dtype):
+  """Prompts of 1300 and 700 tokens in one step each, then the first in portions of 600: in bfloat16 such steps take the
+  recurrences' form for long portions (prepared, then walked in stretches side by side), the library products of the
+  gates' parts and the tensor-core attention over dozens of key tiles; the states they leave carry on into single tokens."""
+  d = luporax_dirs("C")
+  reqs = rc.make_requests(plain.CONFIGS["C"]["vocab"], (1300, 700), seed=17)
+  ref = reference(d, reqs)
+  a, b = reqs["r0"], reqs["r1"]
+  want = lambda lo, hi: list(range(0, hi - lo, 37)) + [hi - lo - 1]
+  trace = [{"step": 0, "entries": [{"id": "r0", "tokens": a[:1290], "want": want(0, 1290)}], "end": []}]
+  trace += [{"step": 1 + j, "entries": [{"id": "r0", "tokens": [a[1290 + j]], "want": [0]}], "end": ["r0"] if j == 9 else []} for j in range(10)]
+  trace.append({"step": 11, "entries": [{"id": "r1", "tokens": b[:600], "want": want(0, 600)}], "end": []})
+  trace.append({"step": 12, "entries": [{"id": "r1", "tokens": b[600:], "want": want(600, 700)}], "end": ["r1"]})
+  runner = runner_for(d, dtype, 1344, 64)
+  got = rc.run_in_process(runner, trace)
+  compare(got, ref, dtype, f"luporax long prompts/{dtype}")
+  runner.cache.check_invariants()
+  runner.runner.check_status()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
