@@ -237,6 +237,11 @@ ATTENTION_CASES = [
   ([(200, 1), (64, 1), (65, 1), (1000, 1)], 8, 2, 64, 64),
   ([(130, 67), (40, 1), (16, 16), (17, 1)], 6, 1, 48, 16),       # heads of 48 on pages of 16: the mma.sync prefill and the cp.async decode kernel
   ([(90, 1), (33, 33)], 3, 3, 24, 8),                            # heads of 24: the generic kernel in both dtypes
+  ([(300, 300), (77, 1), (700, 1), (129, 2)], 8, 1, 128, 64),    # heads of 128, eight query heads on the one key/value head
+  ([(130, 67), (40, 1), (300, 1)], 2, 1, 256, 64),               # heads of 256: beyond the tcgen05 kernel's sizes
+  ([(200, 200), (90, 1)], 4, 4, 32, 64),                         # heads of 32 on pages of 64: no tensor copies of half a row
+  ([(150, 150), (65, 1), (64, 1)], 10, 5, 80, 16),               # heads of 80
+  ([(520, 1), (64, 1)], 32, 2, 64, 64),                          # sixteen query heads on a key/value head: two passes over the tiles
 ]
 
 
@@ -346,3 +351,24 @@ def test_a_block_diagonal_map_part_by_part(dtype, M, parts, K, N):
   out = torch.zeros((parts, M, N), dtype=torch.float32, device=DEV)
   ops.linear_parts(out, x.to(DT[dtype]).to(DEV), w.to(DT[dtype]).to(DEV))
   assert float((out.cpu() - want).abs().max()) <= 2e-5 * float(want.abs().max())
+
+
+@pytest.mark.skipif(DEV == "cpu", reason="two forms of the CUDA kernel")
+@pytest.mark.parametrize("softcap", [0.0, 6.0])
+def test_sigmoid_weights_with_blocks_in_pairs(softcap, monkeypatch):
+  """The tcgen05 prefill kernel with two blocks on a work (what steps of thousands of new tokens take) on shaped scores:
+  the rows of blocks that work alone, and the plain sums."""
+  from miniinfer_b200.kernels import ops
+  nh, nkv, hd, page = 8, 2, 128, 64
+  qkv, kv, bt, batch = make_attention_case([(400, 400), (129, 2), (64, 1)], nh, nkv, hd, page, torch.bfloat16, seed=9, scale_q=0.5)
+  bias = (-2.0 + torch.randn(nh, generator=torch.Generator().manual_seed(2))).to(DEV)
+  outs = []
+  for pairs in ("1", "0"):
+    monkeypatch.setenv("MINIINFER_B200_PREFILL_PAIRS", pairs)
+    out = torch.zeros((qkv.shape[0], nh * hd), dtype=torch.bfloat16, device=DEV)
+    ops.attention(out, qkv, kv, bt, batch, nh, nkv, hd, hd ** -0.5, None, softcap=softcap, score_bias=bias)
+    outs.append(out.float().cpu())
+  want = plain_sigmoid_attention(qkv.cpu(), kv.cpu(), bt.cpu(), batch, nh, nkv, hd, hd ** -0.5, softcap, bias.cpu())
+  for o in outs:
+    assert float((o - want).abs().max()) <= 1.5e-2 * float(want.abs().max())
+  assert float((outs[0] - outs[1]).abs().max()) <= 4e-3 * float(want.abs().max())
