@@ -537,9 +537,14 @@ def linear_parts(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> None:
       _check(lib, lib.mi_gemm_cublas_bf16_batched(_ptr(out), _dt(out), _ptr(x), _ptr(w), M, N, K, B * K, ctypes.c_longlong(K),
                                                   ctypes.c_longlong(N * K), ctypes.c_longlong(M * N), B, _stream()), kernels=0)
       return
-    for b in range(B):
-      linear(out[b], x[:, b * K:(b + 1) * K], w[b])
-    return
+    # while a graph is recorded: torch's products, a part at a time (float32 results where this torch build writes them)
+    if out.dtype == torch.bfloat16 or _mm_f32_out_works(out.device):
+      for b in range(B):
+        if out.dtype == torch.bfloat16:
+          torch.mm(x[:, b * K:(b + 1) * K], w[b].t(), out=out[b])
+        else:
+          torch.mm(x[:, b * K:(b + 1) * K], w[b].t(), out_dtype=torch.float32, out=out[b])
+      return
   linear_batched(out.transpose(0, 1), x.view(M, B, K), w)
 
 
